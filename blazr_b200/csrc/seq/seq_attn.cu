@@ -151,6 +151,73 @@ __global__ void attn_pool_kernel(b200seq_step st, int G, int D, int V, int P, in
                gridDim.y * blockDim.x);
 }
 
+// ---- latent attention: what is cached is one low-rank latent per token plus one rotated key part shared by all heads ---------------------
+// grid (T), 256 threads.  Per token: the latent c = rms_norm(kv[0 .. R)) * w and the rotated shared key part kr = rot(kv[R .. R + Rd))
+// go to the token's pool row [c | kr]; every query head's rotated part goes to its place behind the (still empty) R latent-space
+// columns of the attention's query row, its unrotated part leaves in the activation type for the projection into the latent space
+// (scores are q_nope . (W c) = (W^T q_nope) . c: the keys never leave the latent space), and the gate logits are copied behind the heads.
+// Rotation: interleaved pairs (2i, 2i + 1) over the whole rotated part, angle pos * freq[i], cos and sin times rot_scale.
+// Dynamic shared memory: Rd floats (cos | sin) + 40 of reduction scratch.
+struct LatentPrep {
+    const float* proj;
+    int64_t ldp;
+    int c_col, gate_col;
+    const float* q;
+    int64_t ldq;
+    int H, Dn, Rd, R;
+    const float* norm_w;
+    float eps;
+    const float* freq;
+    float rot_scale;
+    float* kpool;
+    float* Qp;
+    int64_t ldQ;
+    void* qn;
+    int qn_dtype;
+};
+__global__ void latent_prep_kernel(const LatentPrep a, const b200seq_step st, int* err) {
+    extern __shared__ float lsm[];
+    float* cs = lsm;                 // [Rd / 2] cos, [Rd / 2] sin
+    float* red = lsm + a.Rd;
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const int e = st.tok_ent[t], pos = st.tok_pos[t];
+    const int np = a.Rd >> 1, R = a.R, H = a.H, Dn = a.Dn, Rd = a.Rd;
+    for (int i = tid; i < np; i += blockDim.x) {
+        float sn, c;
+        sincosf((float)pos * a.freq[i], &sn, &c);
+        cs[i] = c * a.rot_scale, cs[np + i] = sn * a.rot_scale;
+    }
+    const float* kv = a.proj + (int64_t)t * a.ldp + a.c_col;
+    float ss = 0.f;
+    for (int i = tid; i < R; i += blockDim.x) ss = fmaf(kv[i], kv[i], ss);
+    ss = block_sum(ss, red);         // its barriers also publish cs
+    const float rinv = 1.0f / sqrtf(ss / (float)R + a.eps);
+    const int64_t row = kv_row(st, e, pos, err);
+    if (row >= 0) {
+        float* dst = a.kpool + row * (R + Rd);
+        for (int i = tid; i < R; i += blockDim.x) dst[i] = kv[i] * rinv * a.norm_w[i];
+        for (int i = tid; i < np; i += blockDim.x) {
+            const float u = kv[R + 2 * i], v = kv[R + 2 * i + 1];
+            dst[R + 2 * i] = u * cs[i] - v * cs[np + i];
+            dst[R + 2 * i + 1] = v * cs[i] + u * cs[np + i];
+        }
+    }
+    const float* qr = a.q + (int64_t)t * a.ldq;
+    float* Qt = a.Qp + (int64_t)t * a.ldQ;
+    for (int idx = tid; idx < H * np; idx += blockDim.x) {
+        const int h = idx / np, i = idx - h * np;
+        const float u = qr[(int64_t)h * (Dn + Rd) + Dn + 2 * i], v = qr[(int64_t)h * (Dn + Rd) + Dn + 2 * i + 1];
+        Qt[(int64_t)h * (R + Rd) + R + 2 * i] = u * cs[i] - v * cs[np + i];
+        Qt[(int64_t)h * (R + Rd) + R + 2 * i + 1] = v * cs[i] + u * cs[np + i];
+    }
+    for (int idx = tid; idx < H * Dn; idx += blockDim.x) {
+        const int h = idx / Dn, i = idx - h * Dn;
+        store_act(a.qn, a.qn_dtype, ((int64_t)t * H + h) * Dn + i, qr[(int64_t)h * (Dn + Rd) + i]);
+    }
+    if (a.gate_col >= 0)
+        for (int h = tid; h < H; h += blockDim.x) Qt[(int64_t)H * (R + Rd) + h] = a.proj[(int64_t)t * a.ldp + a.gate_col + h];
+}
+
 // ---- attend -----------------------------------------------------------------------------------------------------------------------
 // One block of 256 threads per (tile of consecutive tokens of one entry, kv head, block of its query heads, split of the keys).
 // Its rows are (token, query head) pairs, RQ = 16 * RT of them (RT = 4: prompt portions; RT = 1: steps of few tokens); the keys the
@@ -176,6 +243,10 @@ struct AttnArgs {
     int out_dtype;
     float* part;   // [T][H][nsplit][V + 2] when nsplit > 1
     int* err;
+    const float* sink;   // [H] or null: exp(sink[h]) joins the soft-max denominator of head h once; it has no key and no value
+    const float* gate;   // gate logits [T][gld] (+ h)
+    int64_t gld;
+    int64_t kld, vld;    // floats per position in kpool / vpool (G * D and G * V, or the key row's width when the values lie inside the key rows)
 };
 
 __device__ __forceinline__ bool attn_find_tile(const b200seq_step& st, int idx, int QT, int& e, int& t0, int& nq) {
@@ -252,7 +323,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
 #pragma unroll
         for (int j = 0; j < VPT; ++j) acc[i][j] = 0.f;
     }
-    const bool vecD = (D & 3) == 0, vecV = (V & 3) == 0;
+    const bool vecD = ((D | a.kld) & 3) == 0, vecV = ((V | a.vld) & 3) == 0;
     // pooled blocks every row of the tile may see (the tile's last row sees the most), then the positions from kbeg to hi
     const int nbmax = (a.pool > 0 && hi - a.window + 1 > 0) ? (hi - a.window + 1) / a.pool : 0;
     const int npt = (nbmax + AT_KT - 1) / AT_KT;
@@ -263,7 +334,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
         const bool in = pooled ? kp < nbmax : kp <= hi;
         const float* src = !in ? nullptr
                            : pooled ? a.vpp + (pooled_row(bt, bs, a.pool, a.ppp, kp) * G + g) * V
-                                    : a.vpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * V;
+                                    : a.vpool + ((int64_t)bt[kp / bs] * bs + kp % bs) * a.vld + (int64_t)g * V;
         if (vecV) {
             for (int c4 = sub; c4 < (VS >> 2); c4 += 4)
                 *reinterpret_cast<float4*>(Vs + k * VS + 4 * c4) = (in && 4 * c4 < V) ? *reinterpret_cast<const float4*>(src + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -282,7 +353,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
             const bool in = pooled ? kp < nbmax : kp <= hi;
             const float* src = !in ? nullptr
                                : pooled ? a.kpp + (pooled_row(bt, bs, a.pool, a.ppp, kp) * G + g) * D
-                                        : a.kpool + (((int64_t)bt[kp / bs] * bs + kp % bs) * G + g) * D;
+                                        : a.kpool + ((int64_t)bt[kp / bs] * bs + kp % bs) * a.kld + (int64_t)g * D;
             if (vecD) {
                 for (int d4 = sub; d4 < (D >> 2); d4 += 4)
                     *reinterpret_cast<float4*>(Ks + k * QS + 4 * d4) = in ? *reinterpret_cast<const float4*>(src + 4 * d4) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -376,8 +447,14 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
         const int t = t0 + tq, h = h0 + hr;
         if (a.nsplit == 1) {
             float gate = 1.f;
-            if (a.gated) gate = sigmoidf_acc(a.qkvg[(int64_t)t * a.ld + a.gate_col + h]);
-            const float f = gate / l[i];
+            if (a.gated) gate = sigmoidf_acc(a.gate[(int64_t)t * a.gld + h]);
+            float den = l[i], resc = 1.f;
+            if (a.sink) {   // the sink's term, under the larger of the two maxima
+                const float sk = a.sink[h], mn = fmaxf(m[i], sk);
+                resc = expf(m[i] - mn);
+                den = fmaf(l[i], resc, expf(sk - mn));
+            }
+            const float f = gate * resc / den;
 #pragma unroll
             for (int jv = 0; jv < VPT / 4; ++jv)
 #pragma unroll
@@ -404,15 +481,15 @@ __global__ void attn_merge_kernel(const AttnArgs a) {
     const int t = blockIdx.x, h = blockIdx.y;
     const int V = a.V, ns = a.nsplit;
     const float* pp = a.part + ((int64_t)t * a.H + h) * ns * (V + 2);
-    float M = -INFINITY;
+    float M = a.sink ? a.sink[h] : -INFINITY;
     for (int s = 0; s < ns; ++s) M = fmaxf(M, pp[s * (V + 2)]);
-    float L = 0.f;
+    float L = a.sink ? expf(a.sink[h] - M) : 0.f;
     for (int s = 0; s < ns; ++s) {
         const float ms = pp[s * (V + 2)];
         if (ms != -INFINITY) L = fmaf(pp[s * (V + 2) + 1], expf(ms - M), L);
     }
     float gate = 1.f;
-    if (a.gated) gate = sigmoidf_acc(a.qkvg[(int64_t)t * a.ld + a.gate_col + h]);
+    if (a.gated) gate = sigmoidf_acc(a.gate[(int64_t)t * a.gld + h]);
     for (int c = threadIdx.x; c < V; c += blockDim.x) {
         float o = 0.f;
         for (int s = 0; s < ns; ++s) {
@@ -452,7 +529,8 @@ using namespace b200seq;
 static int desc_check(const b200seq_attn_desc* d, const char* what) {
     if (!d || d->H < 1 || d->G < 1 || d->H % d->G || d->D < 1 || d->V < 1 || d->q_col < 0 || d->k_col < 0 || d->v_col < 0)
         return fail(B200SEQ_ERR_INVALID_ARG, "%s: bad head counts, sizes or columns", what);
-    if (d->v_col == d->k_col && d->V != d->D) return fail(B200SEQ_ERR_INVALID_ARG, "%s: values taken from the keys need V == D", what);
+    if (!d->latent_v && d->v_col == d->k_col && d->V != d->D) return fail(B200SEQ_ERR_INVALID_ARG, "%s: values taken from the keys need V == D", what);
+    if (d->latent_v && (d->G != 1 || d->V > d->D)) return fail(B200SEQ_ERR_INVALID_ARG, "%s: values inside the key rows need one key head and V <= D", what);
     if (d->rot_dims < 0 || d->rot_dims > d->D || (d->rot_dims & 1) || (d->rot_dims > 0 && !d->rot_freq))
         return fail(B200SEQ_ERR_INVALID_ARG, "%s: rotary dimensions must be even, at most D, with a frequency table", what);
     if (d->pool < 0 || (d->pool > 0 && d->window < 1)) return fail(B200SEQ_ERR_INVALID_ARG, "%s: pooled blocks need a window", what);
@@ -481,8 +559,22 @@ int b200seq_attn_prep_ex(float* proj, int64_t ld, const b200seq_step* st, const 
 }
 
 int b200seq_attn_prep(float* qkvg, int64_t ld, const b200seq_step* st, float* kpool, float* vpool, int H, int G, int D, int V, float qk_eps, void* stream) {
-    const b200seq_attn_desc d{H, G, D, V, 0, H * D, (H + G) * D, -1, 1.f, 0, 0, 0, qk_eps, 0, nullptr, 1.f};
+    const b200seq_attn_desc d{H, G, D, V, 0, H * D, (H + G) * D, -1, 1.f, 0, 0, 0, qk_eps, 0, nullptr, 1.f, nullptr, 0, nullptr, 0};
     return b200seq_attn_prep_ex(qkvg, ld, st, &d, kpool, vpool, nullptr, nullptr, stream);
+}
+
+int b200seq_latent_prep(const float* proj, int64_t ldp, int c_col, int gate_col, const float* q, int64_t ldq, const b200seq_step* st, int H, int Dn, int Rd, int R,
+                        const float* norm_w, float eps, const float* rot_freq, float rot_scale, float* kpool, float* Qp, int64_t ldQ, void* qn, int qn_dtype,
+                        void* stream) {
+    if (!proj || !q || !st || !norm_w || !kpool || !Qp || !qn || H < 1 || Dn < 1 || Rd < 0 || (Rd & 1) || R < 1 || c_col < 0 || (Rd > 0 && !rot_freq))
+        return fail(B200SEQ_ERR_INVALID_ARG, "latent_prep: bad arguments (the rotated part has an even size)");
+    if (ldq < (int64_t)H * (Dn + Rd) || ldQ < (int64_t)H * (R + Rd) + (gate_col >= 0 ? H : 0)) return fail(B200SEQ_ERR_INVALID_ARG, "latent_prep: rows too short");
+    if (qn_dtype != B200SEQ_F32 && qn_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "latent_prep: activation dtype");
+    if (st->T == 0) return 0;
+    const LatentPrep a{proj, ldp, c_col, gate_col, q, ldq, H, Dn, Rd, R, norm_w, eps, rot_freq, rot_scale, kpool, Qp, ldQ, qn, qn_dtype};
+    latent_prep_kernel<<<st->T, 256, (size_t)(Rd + 40) * sizeof(float), (cudaStream_t)stream>>>(a, *st, error_flag_dev());
+    SEQ_LAUNCH_CHECK("latent_prep");
+    return 0;
 }
 
 static int attn_max_keys(const b200seq_step* st, int chunk, int window, int pool) {
@@ -501,7 +593,7 @@ size_t b200seq_attn_scratch_floats(int T, int B, int H, int G, int V, int max_ke
 
 int b200seq_attn_ex(const float* qkvg, int64_t ld, const b200seq_step* st, const b200seq_attn_desc* d, const float* kpool, const float* vpool,
                     const float* kpooled, const float* vpooled, void* out, int out_dtype, float* scratch, size_t scratch_floats, void* stream) {
-    if (!qkvg || !st || !kpool || !vpool || !out) return fail(B200SEQ_ERR_INVALID_ARG, "attn: bad arguments");
+    if (!qkvg || !st || !kpool || !out || !d || (!vpool && !d->latent_v)) return fail(B200SEQ_ERR_INVALID_ARG, "attn: bad arguments");
     if (int rc = desc_check(d, "attn")) return rc;
     if (d->V > 256) return fail(B200SEQ_ERR_INVALID_ARG, "attn: value size <= 256");
     if (d->pool > 0 && (!kpooled || !vpooled)) return fail(B200SEQ_ERR_INVALID_ARG, "attn: pooled blocks need their pools");
@@ -512,7 +604,8 @@ int b200seq_attn_ex(const float* qkvg, int64_t ld, const b200seq_step* st, const
     if (p.nsplit > 1 && (!scratch || scratch_floats < (size_t)st->T * H * p.nsplit * (V + 2))) p.nsplit = 1;
     const int ppp = d->pool > 0 ? (st->block_size + d->pool - 1) / d->pool : 0;
     AttnArgs a{qkvg, ld, kpool, vpool, kpooled, vpooled, d->pool, ppp, d->q_col, d->gate_col, H, G, D, V, p.Rb, p.HB, p.QT, p.nsplit, 0, d->scale, d->chunk, d->window,
-               gated, out, out_dtype, scratch, error_flag_dev()};
+               gated, out, out_dtype, scratch, error_flag_dev(), d->sink, d->gate ? d->gate : qkvg + (gated ? d->gate_col : 0), d->gate ? d->gate_ld : ld, (int64_t)G * D, d->latent_v ? (int64_t)G * D : (int64_t)G * V};
+    if (d->latent_v) a.vpool = kpool;
     const int VPT = V <= 64 ? 4 : (V <= 128 ? 8 : 16);
     const int RQ = 16 * p.RT, QS = ((D + 3) & ~3) + 4;
     size_t smem = ((size_t)(RQ + AT_KT) * QS + (size_t)AT_KT * 16 * VPT + (size_t)RQ * (AT_KT + 4)) * sizeof(float);
@@ -555,7 +648,7 @@ int b200seq_attn_ex(const float* qkvg, int64_t ld, const b200seq_step* st, const
 
 int b200seq_attn(const float* qkvg, int64_t ld, const b200seq_step* st, const float* kpool, const float* vpool, int H, int G, int D, int V, float scale,
                  int chunk, int window, int gated, void* out, int out_dtype, float* scratch, size_t scratch_floats, void* stream) {
-    const b200seq_attn_desc d{H, G, D, V, 0, H * D, (H + G) * D, gated ? (H + G) * D + G * V : -1, scale, chunk, window, 0, -1.f, 0, nullptr, 1.f};
+    const b200seq_attn_desc d{H, G, D, V, 0, H * D, (H + G) * D, gated ? (H + G) * D + G * V : -1, scale, chunk, window, 0, -1.f, 0, nullptr, 1.f, nullptr, 0, nullptr, 0};
     return b200seq_attn_ex(qkvg, ld, st, &d, kpool, vpool, nullptr, nullptr, out, out_dtype, scratch, scratch_floats, stream);
 }
 

@@ -11,7 +11,7 @@ namespace b200seq {
 void count_launch(int n = 1);
 int fail(int code, const char* fmt, ...);
 int cuda_status(cudaError_t e, const char* what);
-int* error_flag_dev();   // device int: bit 0 = KV position outside the block table, bit 1 = bounded wait ran out
+int* error_flag_dev();   // device int: bit 0 = KV position outside the block table, bit 1 = bounded wait ran out, bit 2 = expert table entry out of range
 
 #define SEQ_LAUNCH_CHECK(what)                         \
     do {                                               \
@@ -78,6 +78,6 @@ __device__ __forceinline__ float act_plain(int kind, float z) {
     return z;
 }
 inline bool act_kind_gated(int kind) { return kind == B200SEQ_ACT_SWISH_CLAMP || kind == B200SEQ_ACT_GELU_TANH; }
-inline bool act_kind_known(int kind) { return kind >= B200SEQ_ACT_SWISH_CLAMP && kind <= B200SEQ_ACT_RELU2; }
+inline bool act_kind_known(int kind) { return kind >= B200SEQ_ACT_SWISH_CLAMP && kind <= B200SEQ_ACT_IDENT; }
 
 }  // namespace b200seq

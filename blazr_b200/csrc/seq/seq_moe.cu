@@ -104,6 +104,22 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int64_t ldz, int E
     route_token(z + (int64_t)blockIdx.x * ldz, sm, blockIdx.x, threadIdx.x, E, groups, keep, top, ids, wts, counts);
 }
 
+// choice by table: one thread per (token, choice)
+__global__ void moe_table_route_kernel(const int32_t* __restrict__ table, const int32_t* __restrict__ tok_ids, int T, int E, int top, int32_t* __restrict__ ids,
+                                       float* __restrict__ wts, int32_t* __restrict__ counts, int* err) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= T * top) return;
+    const int t = p / top, j = p - t * top;
+    int e = table[(int64_t)tok_ids[t] * top + j];
+    if (e < 0 || e >= E) {   // a table entry outside the experts: flagged, and kept inside the weights
+        atomicOr(err, 4);
+        e = 0;
+    }
+    ids[p] = e;
+    wts[p] = 1.0f / (float)top;
+    if (counts) atomicAdd(&counts[e], 1);
+}
+
 __device__ __forceinline__ void bf16x8_f32(const uint4 v, float* f);
 template <typename XT>
 __device__ __forceinline__ float ldx(const XT* p);
@@ -365,6 +381,19 @@ int b200seq_moe_route(const float* z, int64_t ldz, int T, int E, int groups, int
     const int g = groups > 1 ? groups : 1;
     moe_route_kernel<<<T, 32, (size_t)(2 * E + g) * sizeof(float), cs>>>(z, ldz, E, g, groups > 1 ? keep : 1, top, ids, wts, counts);
     SEQ_LAUNCH_CHECK("moe_route");
+    return 0;
+}
+
+int b200seq_moe_table_route(const int32_t* table, const int32_t* tok_ids, int T, int E, int top, int32_t* ids, float* wts, int32_t* counts, void* stream) {
+    if (!table || !tok_ids || !ids || !wts || T < 0 || E < 1 || top < 1 || top > E) return fail(B200SEQ_ERR_INVALID_ARG, "moe_table_route: bad arguments");
+    cudaStream_t cs = (cudaStream_t)stream;
+    if (counts) {
+        cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int32_t), cs);
+        if (e != cudaSuccess) return cuda_status(e, "moe_table_route memset");
+    }
+    if (T == 0) return 0;
+    moe_table_route_kernel<<<(T * top + 127) / 128, 128, 0, cs>>>(table, tok_ids, T, E, top, ids, wts, counts, error_flag_dev());
+    SEQ_LAUNCH_CHECK("moe_table_route");
     return 0;
 }
 

@@ -212,7 +212,7 @@ class Engine:
             self.step()
         flags = seqops.error_flags()
         if flags:
-            raise RuntimeError(f"device error flags {flags:#x} (1: KV position outside its block table, 2: a bounded wait ran out)")
+            raise RuntimeError(f"device error flags {flags:#x} (1: KV position outside its block table, 2: a bounded wait ran out, 4: expert table entry out of range)")
         for r in reqs:
             del self.requests[r.rid]
         return [r.output for r in reqs]

@@ -1,10 +1,13 @@
 """Layer-list models: a model is a list of layers, each one token mixer (attention over the paged KV pool, or a state-space
-recurrence with per-slot state) plus an optional feed-forward (dense or a mixture of experts), wrapped in the pieces a design
-switches on.  Two layouts of the residual path exist:
+recurrence with per-slot state, retention, or latent attention) plus an optional feed-forward (dense or a mixture of experts),
+wrapped in the pieces a design switches on.  Three layouts of the residual path exist:
   "streams": sublayers in sequence over several residual streams with learned mixing, grouped RMS norms and a short
              carried-state convolution in front of every sublayer (blazr_b200/fenorax.py);
   "depth":   parallel layers (mixer and feed-forward read the same input through two layer norms), one residual stream whose
-             layer inputs are learned averages over the results of all earlier layers (blazr_b200/gemosun.py).
+             layer inputs are learned averages over the results of all earlier layers (blazr_b200/gemosun.py);
+  "post":    sublayers in sequence that read the residual itself; a sublayer's result is multiplied by a learned sigmoid gate of the
+             residual and the layer norm (weight and bias) comes after the sum, x <- LN(alpha x + gate * result); the mixer reads a
+             blend of the residual with the previous token's (token shift, carried per sequence) (blazr_b200/teselix.py).
 The mechanisms are parameterised (window / chunk / pooled-block size, score scale, unit-norm epsilon, rotary table, gate, state
 size, activation kind, router groups, ...) so that another design can list them in another combination; a design is a function
 config.json -> LayeredConfig.
@@ -40,6 +43,7 @@ class RotarySpec:
     dims: int
     base: float
     yarn: Optional[tuple] = None
+    layout: str = "interleaved"   # "interleaved": pairs (2i, 2i + 1); "half": pairs (i, i + dims / 2)
 
     def table(self):
         """(frequencies float32 [dims / 2], scale of cos and sin)"""
@@ -84,6 +88,35 @@ class SsmSpec:
 
 
 @dataclass
+class RetentionSpec:
+    """linear attention with one fixed decay per head, no soft-max and no denominator: S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t;
+    rotary positions on q and k, k times dim^(-1/2), every head's o divided by its root mean square, times silu(gate), then the output projection"""
+    heads: int
+    dim: int                 # per-head query / key size
+    vdim: int                # per-head value size
+    decay: List[float] = field(default_factory=list)
+    rot: Optional[RotarySpec] = None
+
+
+@dataclass
+class LatentAttentionSpec:
+    """attention whose queries, keys and values come out of low-rank latents: c_q = rms_norm(W_dq h), q = W_uq c_q laid out per head as
+    [dim unrotated | rot_dim rotated]; W_dkv h = [kv_rank latent (rms-normed: c) | rot_dim rotated key part shared by all heads]; per head the
+    unrotated key is W_uk c and the value W_uv c.  Only c and the rotated key part are cached.  Causal soft-max over all earlier positions with
+    an optional learned sink per head in the denominator and an optional sigmoid gate per head on the output."""
+    heads: int
+    dim: int                 # unrotated query / key dimensions per head
+    rot_dim: int             # rotated dimensions per head
+    vdim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    rot: Optional[RotarySpec] = None
+    sink: bool = True
+    gated: bool = True
+
+
+@dataclass
 class DenseFfSpec:
     ff: int
     limit: float = 0.0
@@ -102,16 +135,22 @@ class MoeFfSpec:
     ff: int
     groups: int = 1
     keep: int = 1
-    act: str = "relu2"
+    act: str = "relu2"       # a plain kind: down(act(up h)); a gated kind ("swish_clamp"): down(act(gate h, up h)) with limit / alpha / up_shift
     shared_ff: int = 0       # 0: no shared expert
     shared_gate: bool = True
+    router: str = "sigmoid"  # "sigmoid": learned router as above; "table": no router, a table [vocab, top] indexed by the token id names the experts, each weighted 1 / top
+    limit: float = 0.0
+    alpha: float = 1.702
+    up_shift: float = 1.0
+    shared_limit: float = 0.0
 
 
 @dataclass
 class LayerSpec:
-    kind: str                # "attention" | "ssm"
+    kind: str                # "attention" | "ssm" | "retention" | "latent_attention"
     mixer: object
     ff: Optional[object]     # DenseFfSpec | MoeFfSpec | None
+    weights_of: Optional[int] = None   # layout "post": the layer has no tensors of its own and uses those of this (earlier) layer, with its own cache / state
 
 
 @dataclass
@@ -128,6 +167,7 @@ class LayeredConfig:
     layout: str = "streams"  # "streams" | "depth" (see the module text)
     tied_head: bool = True   # the output projection is the embedding table; False: a tensor "head"
     depth_average: bool = True   # layout "depth": layer i has weights "l<i>.dwa" [i + 2] over the embedding and the results of layers 0..i
+    post_alpha: float = 1.0      # layout "post": weight of the residual in the sum that is normed
 
 
 class _Workspace:
@@ -157,6 +197,16 @@ class _Workspace:
             # the feed-forward branch runs beside the mixer on a second stream: it keeps its own intermediates
             self.ff_inner = torch.empty((cap, max(1, model.max_ff_inner)), **act)
             self.ff_proj = torch.empty((cap, max(1, model.max_ff_proj)), **f32)
+        if cfg.layout == "post":        # shifted activations, gate logits, buffers of the latent-attention mixer, the shared expert's intermediates
+            self.a2 = torch.empty((cap, W), **act)
+            self.zg = torch.empty((cap, W), **f32)
+            self.q = torch.empty((cap, max(1, model.max_q)), **f32)
+            self.Qp = torch.empty((cap, max(1, model.max_qp)), **f32)
+            self.qn = torch.empty((cap, max(1, model.max_qn)), **act)
+            self.oup = torch.empty((cap, max(1, model.max_inner)), **act)
+            self.ff_inner = torch.empty((cap, max(1, model.max_ff_inner)), **act)
+            self.ff_proj = torch.empty((cap, max(1, model.max_ff_proj)), **f32)
+            self.head_ids = {H: (torch.arange(cap * H, dtype=torch.int32) % H).to(dev) for H in model.latent_heads}
         mo = model.moe_dims
         if mo is not None:              # mixture of experts: router logits, choices, sort, per-pair intermediates
             E1, top, F = mo
@@ -169,6 +219,7 @@ class _Workspace:
             self.moe_order = torch.empty((cap * top,), **i32)
             self.moe_slot = torch.empty((cap * top,), **i32)
             self.moe_act = torch.empty((cap * top, F), **act)
+            self.moe_z2 = torch.empty((cap * top, 2 * F), **f32) if model.moe_gated else None      # gate | up products of gated experts
             self.moe_ys = torch.empty((cap * top, W), **f32)
             self.moe_sh = torch.empty((cap, W), **f32)
             self.moe_xs = torch.empty((cap * top, W), **act) if model.act_dtype == torch.bfloat16 else None   # tokens' rows in sorted pair order
@@ -222,14 +273,15 @@ class LayeredModel:
         def hc(pre):    # (in [S], post = out [S] | mix [S, S])
             return vec(pre + "in"), torch.cat([get(pre + "out").float().reshape(-1), get(pre + "mix").float().reshape(-1)]).contiguous().to(dev)
 
-        if cfg.layout not in ("streams", "depth"):
+        if cfg.layout not in ("streams", "depth", "post"):
             raise ValueError(f"unknown residual layout {cfg.layout}")
-        depth = cfg.layout == "depth"
-        if depth and (S != 1 or cfg.canon_taps > 1):
-            raise ValueError("the depth-averaged layout has one residual stream and no carried convolution")
+        depth, post = cfg.layout == "depth", cfg.layout == "post"
+        if (depth or post) and (S != 1 or cfg.canon_taps > 1):
+            raise ValueError("the depth-averaged and post-norm layouts have one residual stream and no carried convolution")
         self.embed = lin("embed")
         self.head = self.embed if cfg.tied_head else lin("head")
         self.final_norm = vec("final.norm")
+        self.final_bias = vec("final.norm.b") if post else None
         if tuple(self.embed.shape) != (cfg.vocab, W) or tuple(self.head.shape) != (cfg.vocab, W) or self.final_norm.numel() != W:
             raise ValueError("embedding / head / final norm shapes do not fit the configuration")
         self.ones_in = torch.ones(S, dtype=torch.float32, device=dev)
@@ -237,8 +289,14 @@ class LayeredModel:
         self.max_proj = self.max_xbc = self.max_inner = 1
         self.max_ff_inner = self.max_ff_proj = 1      # depth layout: sizes of the feed-forward branch's own intermediates
         self.moe_dims = None      # (experts + 1, top, expert ff): largest over the layers
+        self.moe_gated = False    # some layer's experts have a gate branch
+        self.max_q = self.max_qp = self.max_qn = 1      # latent attention: query rows, latent-space query rows, unrotated query parts
+        self.latent_heads = set()
         self.weight_bytes = self.embed.numel() * 2 + (0 if cfg.tied_head else self.head.numel() * 2)
         for i, ls in enumerate(cfg.layers):
+            if post:
+                self.layers.append(self._post_layer(i, ls, lin, vec, get))
+                continue
             L: Dict[str, object] = {"spec": ls}
             p = f"l{i}."
             L["norm1"] = vec(p + "norm1")
@@ -289,8 +347,8 @@ class LayeredModel:
             self.weight_bytes += (L["w_in"].numel() + L["w_o"].numel()) * 2
             if isinstance(ls.ff, MoeFfSpec):
                 f = ls.ff
-                if f.act not in ("relu2",) or seqops.ACT_KINDS[f.act] in seqops.ACT_GATED:
-                    raise ValueError(f"layer {i}: expert activation {f.act} is not supported")
+                if f.act not in ("relu2",) or seqops.ACT_KINDS[f.act] in seqops.ACT_GATED or f.router != "sigmoid":
+                    raise ValueError(f"layer {i}: expert activation {f.act} / router {f.router} is not supported in this layout")
                 if f.top > f.experts or (f.groups > 1 and (f.experts % f.groups or not 1 <= f.keep <= f.groups or f.keep * (f.experts // f.groups) < f.top)):
                     raise ValueError(f"layer {i}: router groups / top do not fit the expert count")
                 L["norm2"] = vec(p + "norm2")
@@ -339,6 +397,152 @@ class LayeredModel:
         self.overlap_branches = True     # depth layout: mixer and feed-forward of a layer on two streams
         self._side = self._side2 = None
 
+    # ---- layout "post": weights of one layer -------------------------------------------------------------------------------------------
+    def _post_layer(self, i: int, ls: "LayerSpec", lin, vec, get) -> Dict[str, object]:
+        cfg, dev, W = self.cfg, self.dev, self.cfg.width
+        m, f = ls.mixer, ls.ff
+        if ls.weights_of is not None:     # the tensors of an earlier layer; cache and state are this layer's own (allocate())
+            j = ls.weights_of
+            if not 0 <= j < i or cfg.layers[j].weights_of is not None:
+                raise ValueError(f"layer {i}: weights_of must name an earlier layer that has tensors of its own")
+            if cfg.layers[j].kind != ls.kind or cfg.layers[j].mixer != m or cfg.layers[j].ff != f:
+                raise ValueError(f"layer {i}: a layer that shares weights has the sizes of the layer it shares them with")
+            L = dict(self.layers[j])
+            L["spec"] = ls
+            self._post_sizes(L, ls)
+            return L
+        L: Dict[str, object] = {"spec": ls}
+        p = f"l{i}."
+        sub = (1, 2) if f is not None else (1,)
+        for q in sub:
+            L[f"norm{q}"], L[f"norm{q}_b"] = vec(p + f"norm{q}"), vec(p + f"norm{q}.b")
+            L[f"rg{q}"], L[f"rg{q}_b"] = lin(p + f"rg{q}"), vec(p + f"rg{q}.b")
+            if L[f"norm{q}"].numel() != W or L[f"norm{q}_b"].numel() != W or tuple(L[f"rg{q}"].shape) != (W, W) or L[f"rg{q}_b"].numel() != W:
+                raise ValueError(f"layer {i}: norm / residual-gate tensor shapes do not fit the width")
+            self.weight_bytes += L[f"rg{q}"].numel() * 2
+        L["shift"] = vec(p + "shift")
+        if L["shift"].numel() != W:
+            raise ValueError(f"layer {i}: token-shift weight does not fit the width")
+
+        def rotary(rot, size, what):
+            if rot is None:
+                return None, 1.0
+            if rot.dims < 2 or rot.dims % 2 or rot.dims > size:
+                raise ValueError(f"layer {i}: rotary dimensions must be even and at most {what}")
+            fr, scale = rot.table()
+            return torch.from_numpy(fr).to(dev), scale
+
+        if ls.kind == "retention":
+            import math
+            H, D, V = m.heads, m.dim, m.vdim
+            L["w_in"] = lin(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g")
+            L["w_o"] = lin(p + "mix.o")
+            if tuple(L["w_in"].shape) != (2 * H * D + 2 * H * V, W) or tuple(L["w_o"].shape) != (W, H * V) or len(m.decay) != H:
+                raise ValueError(f"layer {i}: retention tensor shapes / decay list do not fit the configuration")
+            if any(not 0.0 < float(d) <= 1.0 for d in m.decay):
+                raise ValueError(f"layer {i}: decays lie in (0, 1]")
+            L["decay"] = torch.tensor([[float(d) for d in m.decay], [math.log2(float(d)) for d in m.decay]], dtype=torch.float64).to(torch.float32).to(dev)
+            L["rot_freq"], rot_scale = rotary(m.rot, D, "the key size")
+            if m.rot is not None and m.rot.layout not in ("half", "interleaved"):
+                raise ValueError(f"layer {i}: unknown rotary layout {m.rot.layout}")
+            L["desc"] = seqops.retention_desc(H, D, V, L["decay"], cfg.eps, float(D) ** -0.5, rot_freq=L["rot_freq"],
+                                              rot_half=m.rot is not None and m.rot.layout == "half", rot_scale=rot_scale)
+        elif ls.kind == "latent_attention":
+            H, Dn, Rd, V, R, Rq = m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank
+            if m.rot is not None and (m.rot.dims != Rd or m.rot.layout != "interleaved"):
+                raise ValueError(f"layer {i}: the rotated part turns as a whole, in interleaved pairs")
+            if (m.rot is None) != (Rd == 0):
+                raise ValueError(f"layer {i}: a rotated part needs rotary constants (and the other way round)")
+            L["w_in"] = lin(*([p + "mix.dq", p + "mix.dkv"] + ([p + "mix.g"] if m.gated else [])))     # one projection of the shifted input: c_q | c, k_rot | gates
+            L["dq_norm"], L["kv_norm"] = vec(p + "mix.dq.norm"), vec(p + "mix.dkv.norm")
+            L["w_uq"], L["w_o"] = lin(p + "mix.uq"), lin(p + "mix.o")
+            uk, uv = lin(p + "mix.uk"), lin(p + "mix.uv")
+            if tuple(L["w_in"].shape) != (Rq + R + Rd + (H if m.gated else 0), W) or tuple(L["w_uq"].shape) != (H * (Dn + Rd), Rq) or tuple(uk.shape) != (H * Dn, R) \
+                    or tuple(uv.shape) != (H * V, R) or tuple(L["w_o"].shape) != (W, H * V) or L["dq_norm"].numel() != Rq or L["kv_norm"].numel() != R:
+                raise ValueError(f"layer {i}: latent-attention tensor shapes do not fit the configuration")
+            L["w_ukT"] = uk.view(H, Dn, R).transpose(1, 2).contiguous()      # [H][R][Dn]: the query's way into the latent space
+            L["w_uv"] = uv.view(H, V, R).contiguous()
+            L["sink"] = vec(p + "mix.sink") if m.sink else None
+            if m.sink and L["sink"].numel() != H:
+                raise ValueError(f"layer {i}: one sink per head expected")
+            L["rot_freq"], L["rot_scale"] = rotary(m.rot, max(Rd, 2), "the rotated part")
+            L["desc"] = seqops.latent_attn_desc(H, R, Rd, m.scale, gated=m.gated, sink=L["sink"])
+            self.weight_bytes += (L["w_uq"].numel() + uk.numel() + uv.numel()) * 2
+        else:
+            raise ValueError(f"layer {i}: mixer kind {ls.kind} is not wired into the post-norm layout")
+        self.weight_bytes += (L["w_in"].numel() + L["w_o"].numel()) * 2
+
+        def gate_up(pre, ff):      # rows alternate (gate j, up j): the pair meets in one warp / neighbouring lanes
+            gu = lin(pre + "gate", pre + "up")
+            if tuple(gu.shape) != (2 * ff, W):
+                raise ValueError(f"layer {i}: {pre}gate / up shapes do not fit the configuration")
+            return gu.view(2, ff, W).transpose(0, 1).reshape(2 * ff, W).contiguous()
+
+        if isinstance(f, MoeFfSpec):
+            if f.act not in seqops.ACT_KINDS or not 1 <= f.top <= f.experts:
+                raise ValueError(f"layer {i}: expert activation {f.act} / top {f.top} is not supported")
+            gated = seqops.ACT_KINDS[f.act] in seqops.ACT_GATED
+            if f.router == "table":
+                t = get(p + "mlp.table")
+                if t.dtype not in (torch.int32, torch.int64) or tuple(t.shape) != (cfg.vocab, f.top):
+                    raise ValueError(f"layer {i}: the expert table is an integer tensor [vocab, top]")
+                if int(t.min()) < 0 or int(t.max()) >= f.experts:
+                    raise ValueError(f"layer {i}: the expert table names an expert outside 0..{f.experts - 1}")
+                L["table"] = t.to(torch.int32).contiguous().to(dev)
+            elif f.router == "sigmoid":
+                router = [p + "mlp.router"] + ([p + "mlp.shared.sg"] if f.shared_ff and f.shared_gate else [])
+                L["w_router"] = lin(*router)
+                self.weight_bytes += L["w_router"].numel() * 2
+            else:
+                raise ValueError(f"layer {i}: unknown router kind {f.router}")
+            if gated:
+                L["w_eup"] = torch.stack([gate_up(p + f"mlp.e{e}.", f.ff) for e in range(f.experts)]).contiguous()
+                self.moe_gated = True
+            else:
+                L["w_eup"] = torch.stack([lin(p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
+            L["w_edown"] = torch.stack([lin(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
+            if tuple(L["w_eup"].shape[1:]) != ((2 if gated else 1) * f.ff, W) or tuple(L["w_edown"].shape[1:]) != (W, f.ff):
+                raise ValueError(f"layer {i}: expert tensor shapes do not fit the configuration")
+            self.weight_bytes += (L["w_eup"].numel() + L["w_edown"].numel()) * 2
+            if f.shared_ff:
+                L["w_sup"] = gate_up(p + "mlp.shared.", f.shared_ff) if gated else lin(p + "mlp.shared.up")
+                L["w_sdown"] = lin(p + "mlp.shared.down")
+                if L["w_sup"].shape[1] != W or tuple(L["w_sdown"].shape) != (W, f.shared_ff):
+                    raise ValueError(f"layer {i}: shared expert tensor shapes do not fit the configuration")
+                self.weight_bytes += (L["w_sup"].numel() + L["w_sdown"].numel()) * 2
+        elif f is not None:
+            if f.act not in seqops.ACT_KINDS or seqops.ACT_KINDS[f.act] not in seqops.ACT_GATED:
+                raise ValueError(f"layer {i}: dense feed-forward activation {f.act} is not a gated kind")
+            L["w_gu"] = gate_up(p + "mlp.", f.ff)
+            L["w_down"] = lin(p + "mlp.down")
+            if tuple(L["w_down"].shape) != (W, f.ff):
+                raise ValueError(f"layer {i}: feed-forward tensor shapes do not fit the configuration")
+            self.weight_bytes += (L["w_gu"].numel() + L["w_down"].numel()) * 2
+        self._post_sizes(L, ls)
+        return L
+
+    def _post_sizes(self, L, ls: "LayerSpec") -> None:
+        """largest intermediates over the layers (workspace sizes)"""
+        m, f = ls.mixer, ls.ff
+        self.max_proj = max(self.max_proj, L["w_in"].shape[0])
+        if ls.kind == "retention":
+            self.max_inner = max(self.max_inner, m.heads * m.vdim)
+        else:
+            self.max_inner = max(self.max_inner, m.heads * m.vdim, m.heads * m.kv_rank, m.q_rank)
+            self.max_q = max(self.max_q, m.heads * (m.dim + m.rot_dim), m.vdim)
+            self.max_qp = max(self.max_qp, m.heads * (m.kv_rank + m.rot_dim))
+            self.max_qn = max(self.max_qn, m.heads * m.dim)
+            self.latent_heads.add(m.heads)
+        if isinstance(f, MoeFfSpec):
+            md = self.moe_dims or (1, 1, 1)
+            self.moe_dims = (max(md[0], f.experts + 1), max(md[1], f.top), max(md[2], f.ff))
+            if f.shared_ff:
+                self.max_ff_inner = max(self.max_ff_inner, f.shared_ff)
+                self.max_ff_proj = max(self.max_ff_proj, 2 * f.shared_ff)
+        elif f is not None:
+            self.max_ff_inner = max(self.max_ff_inner, f.ff)
+            self.max_ff_proj = max(self.max_ff_proj, 2 * f.ff)
+
     # ---- cache and state -------------------------------------------------------------------------------------------------------
     def allocate(self, num_blocks: int, block_size: int, max_seqs: int, max_seq_tokens: int) -> None:
         """KV pools for `num_blocks` pages, state for `max_seqs` slots; block tables hold up to max_seq_tokens positions"""
@@ -354,7 +558,13 @@ class LayeredModel:
                 L["canon1_state"] = torch.zeros((max_seqs, max(hist, 1), cfg.width), **f32)
                 if ls.ff is not None:
                     L["canon2_state"] = torch.zeros((max_seqs, max(hist, 1), cfg.width), **f32)
-            if ls.kind == "attention":
+            if cfg.layout == "post":
+                L["shift_state"] = torch.zeros((max_seqs, cfg.width), **f32)      # the mixer input of the sequence's last token
+            if ls.kind == "retention":
+                L["ret_state"] = torch.zeros((max_seqs, m.heads, m.dim, m.vdim), **f32)
+            elif ls.kind == "latent_attention":       # one row [latent | rotated key part] per position; keys and values of all heads come out of it
+                L["kpool"] = torch.zeros((max(1, num_blocks), block_size, m.kv_rank + m.rot_dim), **f32)
+            elif ls.kind == "attention":
                 L["kpool"] = torch.zeros((max(1, num_blocks), block_size, m.kv_heads, m.dim), **f32)
                 L["vpool"] = torch.zeros((max(1, num_blocks), block_size, m.kv_heads, m.vdim), **f32)
                 if m.pool > 0:      # mean key / value of every block of `pool` positions, kept in the page of the block's first position
@@ -375,6 +585,14 @@ class LayeredModel:
             m = L["spec"].mixer
             if L["spec"].kind == "ssm":
                 need = max(need, seqops.ssm_scratch_floats(cap, self.max_seqs, m.heads, m.vdim, m.state))
+            elif L["spec"].kind == "retention":
+                need = max(need, seqops.retention_scratch_floats(cap, self.max_seqs, m.heads, m.dim, m.vdim))
+            elif L["spec"].kind == "latent_attention":
+                key = ("latent", m.heads, m.kv_rank)
+                if key not in seen:
+                    seen.add(key)
+                    ctx = self.max_blocks * self.block_size
+                    need = max([need] + [seqops.attn_scratch_floats(T, 1, m.heads, 1, m.kv_rank, ctx) for T in range(1, cap + 1)])
             else:
                 ctx = keys = self.max_blocks * self.block_size
                 keys = min(keys, m.chunk) if m.chunk > 0 else keys
@@ -387,7 +605,7 @@ class LayeredModel:
         return need
 
     def cache_bytes(self) -> int:
-        keys = ("canon1_state", "canon2_state", "kpool", "vpool", "kpooled", "vpooled", "conv_state", "ssm_state")
+        keys = ("canon1_state", "canon2_state", "kpool", "vpool", "kpooled", "vpooled", "conv_state", "ssm_state", "shift_state", "ret_state")
         return sum(L[k].numel() * 4 for L in self.layers for k in keys if k in L)
 
     def _workspace(self, T: int) -> _Workspace:
@@ -460,6 +678,8 @@ class LayeredModel:
     def _run(self, ws: _Workspace, T: int, B: int, R: int, sample: bool, debug_layers: Optional[list]) -> None:
         if self.cfg.layout == "depth":
             self._run_depth(ws, T, B, R, sample, debug_layers)
+        elif self.cfg.layout == "post":
+            self._run_post(ws, T, B, R, debug_layers)
         else:
             self._run_streams(ws, T, B, R, sample, debug_layers)
         if R:
@@ -537,6 +757,97 @@ class LayeredModel:
         if not n and R:
             ops.depth_norm(x0, ws.fin[:R], self.final_norm, cfg.eps, rows=ws.view("want")[:R])
 
+    def _run_post(self, ws: _Workspace, T: int, B: int, R: int, debug_layers: Optional[list]) -> None:
+        """sublayers in sequence over one residual x (f32): mixer(shifted x) and feed-forward(x), each times sigmoid(rg x + b), each followed by
+        the layer norm of alpha x + gated result.  Between sublayers ONE kernel: gate, sum, norm, the next sublayer's input in the activation type,
+        the shift state of the mixer it closes and - in steps of single tokens - the token shift of the next mixer."""
+        cfg, ops = self.cfg, seqops
+        st = self._desc(ws, T, B)
+        x, a, ash, y, zg = ws.h[:T], ws.a[:T], ws.a2[:T], ws.y[:T], ws.zg[:T]
+        ops.embed_streams(self.embed, ws.view("ids"), cfg.embed_scale, x.view(T, 1, cfg.width))
+        n = len(self.layers)
+        single = T == B
+        if n:
+            ops.token_shift(x, self.layers[0]["shift"], self.layers[0]["shift_state"], st, a, ash)
+        for i, L in enumerate(self.layers):
+            ls: LayerSpec = L["spec"]
+            ops.linear(a, L["rg1"], zg)
+            if ls.kind == "retention":
+                self._retention(L, ls.mixer, ws, st, T, ash, y)
+            else:
+                self._latent_attention(L, ls.mixer, ws, st, T, ash, y)
+            close = dict(y=y, zg=zg, alpha=cfg.post_alpha, x_out=x, a_out=a, step=st)
+            q = 1
+            if ls.ff is not None:
+                ops.post_norm(x, L["norm1"], L["norm1_b"], cfg.eps, gate_b=L["rg1_b"], state_out=L["shift_state"], **close)
+                ops.linear(a, L["rg2"], zg)
+                if isinstance(ls.ff, MoeFfSpec):
+                    self._moe_ff(L, ls.ff, ws, T, a, y)
+                else:
+                    self._dense_ff(L, ls.ff, ws, T, a, y, inner=ws.ff_inner, proj=ws.ff_proj)
+                q = 2
+            else:
+                close["state_out"] = L["shift_state"]
+            nxt = self.layers[i + 1] if i + 1 < n else None
+            if nxt is not None and single:
+                close.update(next_mu=nxt["shift"], next_state=nxt["shift_state"], a_shift_out=ash)
+            ops.post_norm(x, L[f"norm{q}"], L[f"norm{q}_b"], cfg.eps, gate_b=L[f"rg{q}_b"], **close)
+            if nxt is not None and not single:
+                ops.token_shift(x, nxt["shift"], nxt["shift_state"], st, None, ash)
+            if debug_layers is not None:
+                debug_layers.append(x.cpu())
+        if R:
+            ops.post_norm(x, self.final_norm, self.final_bias, cfg.eps, rows=ws.view("want")[:R], a_out=ws.fin[:R])
+
+    def _retention(self, L, m: RetentionSpec, ws: _Workspace, st, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
+        proj = ws.proj[:T, :L["w_in"].shape[0]]
+        seqops.linear(a, L["w_in"], proj)
+        o = ws.inner_a.view(-1)[:T * m.heads * m.vdim].view(T, m.heads * m.vdim)
+        seqops.retention(proj, st, L["desc"], L["ret_state"], o, ws.scratch)
+        seqops.linear(o, L["w_o"], y)
+
+    def _latent_attention(self, L, m: LatentAttentionSpec, ws: _Workspace, st, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
+        H, Dn, Rd, V, R, Rq = m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank
+        eps = self.cfg.eps
+        proj = ws.proj[:T, :L["w_in"].shape[0]]
+        seqops.linear(a, L["w_in"], proj)                                   # c_q | c, k_rot | gate logits
+        cq = ws.inner_a.view(-1)[:T * Rq].view(T, Rq)
+        seqops.group_rmsnorm(proj[:, :Rq], L["dq_norm"], 1, eps, cq)
+        q = ws.q.view(-1)[:T * H * (Dn + Rd)].view(T, H * (Dn + Rd))
+        seqops.linear(cq, L["w_uq"], q)
+        Qp = ws.Qp.view(-1)[:T * H * (R + Rd)].view(T, H * (R + Rd))
+        qn = ws.qn.view(-1)[:T * H * Dn].view(T * H, Dn)
+        seqops.latent_prep(proj, Rq, -1, q, st, H, Dn, Rd, R, L["kv_norm"], eps, L["rot_freq"], L["rot_scale"], L["kpool"], Qp, qn)
+        # the unrotated query parts enter the latent space head by head: Qp[t][h][:R] = W_uk[h]^T q_nope[t][h]
+        self._head_linear(ws, T, H, qn, L["w_ukT"], Qp.view(T * H, R + Rd)[:, :R], None)
+        o = ws.inner_a.view(-1)[:T * H * R].view(T, H * R)
+        gate = proj[:, Rq + R + Rd:] if m.gated else None
+        seqops.attn_ex(Qp, st, L["desc"], L["kpool"], None, o, ws.scratch, gate=gate)
+        up = ws.oup.view(-1)[:T * H * V].view(T, H * V)
+        self._head_linear(ws, T, H, o.view(T * H, R), L["w_uv"], up.view(T * H, V), ws.q)      # values leave the latent space after the weighted sum
+        seqops.linear(up, L["w_o"], y)
+
+    HEAD_ROW_PAIRS = 64     # up to this many (token, head) pairs one launch streams every head's weight per pair; more: one product per head
+
+    def _head_linear(self, ws: _Workspace, T: int, H: int, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tmp: Optional[torch.Tensor]) -> None:
+        """out[t * H + h] = w[h] . x[t * H + h] for every (token, head): x [T * H, K] rows, w bf16 [H, N, K], out [T * H, N] rows (f32: the product;
+        activation type: the product written in that type, `tmp` holds the f32 product where no fused path takes the step)"""
+        ops = seqops
+        pairs = T * H
+        to_act = out.dtype != torch.float32 or tmp is not None
+        if pairs <= self.HEAD_ROW_PAIRS:
+            ops.moe_linear(x, 0, w, ws.head_ids[H], None, None, pairs, ops.ACT_IDENT if to_act else ops.ACT_NONE, out)
+            return
+        K, N = x.shape[1], out.shape[1]
+        xs, os_ = x.stride(0), out.stride(0)
+        for h in range(H):
+            xh = x.as_strided((T, K), (H * xs, 1), x.storage_offset() + h * xs)
+            oh = out.as_strided((T, N), (H * os_, 1), out.storage_offset() + h * os_)
+            if to_act:
+                self._proj_act(tmp, T, xh, w[h], ops.ACT_IDENT, oh)
+            else:
+                ops.linear(xh, w[h], oh)
+
     def _run_streams(self, ws: _Workspace, T: int, B: int, R: int, sample: bool, debug_layers: Optional[list]) -> None:
         cfg = self.cfg
         ops = seqops
@@ -613,16 +924,23 @@ class LayeredModel:
         ops = seqops
         E, top = f.experts, f.top
         gated_shared = bool(f.shared_ff and f.shared_gate)
-        z = ws.moe_z[:T, :L["w_router"].shape[0]]
         pairs = T * top
         rows_form = pairs <= self.MOE_ROW_PAIRS
-        if T <= 8 and rows_form:        # few tokens: projection and choice in one kernel
-            ops.moe_router(a, L["w_router"], E, f.groups, f.keep, top, z, ws.moe_ids, ws.moe_wts)
+        z = None
+        if f.router == "table":         # no router: the token id names the experts
+            ops.moe_table_route(L["table"], ws.view("ids"), T, E, top, ws.moe_ids, ws.moe_wts, None if rows_form else ws.moe_cnt)
         else:
-            ops.linear(a, L["w_router"], z)
-            ops.moe_route(z, E, f.groups, f.keep, top, ws.moe_ids, ws.moe_wts, None if rows_form else ws.moe_cnt)
+            z = ws.moe_z[:T, :L["w_router"].shape[0]]
+            if T <= 8 and rows_form:        # few tokens: projection and choice in one kernel
+                ops.moe_router(a, L["w_router"], E, f.groups, f.keep, top, z, ws.moe_ids, ws.moe_wts)
+            else:
+                ops.linear(a, L["w_router"], z)
+                ops.moe_route(z, E, f.groups, f.keep, top, ws.moe_ids, ws.moe_wts, None if rows_form else ws.moe_cnt)
         kind = ops.ACT_KINDS[f.act]
         mid = ws.moe_act.view(-1)[:pairs * f.ff].view(pairs, f.ff)
+        up_out, up_kind = mid, kind
+        if kind in ops.ACT_GATED:       # gated experts: the gate | up product of every pair (rows alternate), then the activation
+            up_out, up_kind = ws.moe_z2.view(-1)[:pairs * 2 * f.ff].view(pairs, 2 * f.ff), ops.ACT_NONE
         ys = ws.moe_ys[:pairs]
         if rows_form:
             order = offs = slot = None
@@ -632,9 +950,11 @@ class LayeredModel:
         if not rows_form and ws.moe_xs is not None and ops.tc_usable(a, a.shape[1]) and f.ff % 8 == 0:
             xs = ws.moe_xs[:pairs]                  # tensor-core tiles fetch contiguous rows: put the tokens' rows in sorted order first
             ops.moe_gather(a, top, order, pairs, xs)
-            ops.moe_linear(xs, 0, L["w_eup"], ws.moe_ids, order, offs, pairs, kind, mid)
+            ops.moe_linear(xs, 0, L["w_eup"], ws.moe_ids, order, offs, pairs, up_kind, up_out)
         else:
-            ops.moe_linear(a, top, L["w_eup"], ws.moe_ids, order, offs, pairs, kind, mid)
+            ops.moe_linear(a, top, L["w_eup"], ws.moe_ids, order, offs, pairs, up_kind, up_out)
+        if up_out is not mid:
+            ops.act(up_out, kind, mid, f.limit, f.alpha, f.up_shift)
         ops.moe_linear(mid, 0, L["w_edown"], ws.moe_ids, order, offs, pairs, ops.ACT_NONE, ys)
         sh = None
         if shared_done is not None:
@@ -642,11 +962,11 @@ class LayeredModel:
             sh = ws.moe_sh[:T]
         elif f.shared_ff:
             sh = self._shared_expert(L, f, ws, T, a)
-        ops.moe_combine(ys, ws.moe_wts, slot, T, top, sh, z[:, E] if gated_shared else None, y)
+        ops.moe_combine(ys, ws.moe_wts, slot, T, top, sh, z[:, E] if gated_shared and z is not None else None, y)
 
     def _shared_expert(self, L, f: "MoeFfSpec", ws: _Workspace, T: int, a: torch.Tensor) -> torch.Tensor:
         smid = ws.ff_inner.view(-1)[:T * f.shared_ff].view(T, f.shared_ff)
-        self._proj_act(ws.ff_proj, T, a, L["w_sup"], seqops.ACT_KINDS[f.act], smid)
+        self._proj_act(ws.ff_proj, T, a, L["w_sup"], seqops.ACT_KINDS[f.act], smid, f.shared_limit, f.alpha, f.up_shift)
         sh = ws.moe_sh[:T]
         seqops.linear(smid, L["w_sdown"], sh)
         return sh

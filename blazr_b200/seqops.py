@@ -23,7 +23,7 @@ LIB_PATH = os.environ.get("B200SEQ_LIB") or os.path.join(_HERE, "lib", "libb200s
 
 F32, BF16 = 0, 2
 CONV_RESIDUAL, CONV_SILU = 1, 2
-ACT_SWISH_CLAMP, ACT_GELU_TANH, ACT_RELU2 = 0, 1, 2   # gated: clamped swish, tanh-gelu gate; plain: squared relu
+ACT_SWISH_CLAMP, ACT_GELU_TANH, ACT_RELU2, ACT_IDENT = 0, 1, 2, 3   # gated: clamped swish, tanh-gelu gate; plain: squared relu, the product itself
 ACT_NONE = -1
 ACT_KINDS = {"swish_clamp": ACT_SWISH_CLAMP, "gelu_tanh": ACT_GELU_TANH, "relu2": ACT_RELU2}
 ACT_GATED = (ACT_SWISH_CLAMP, ACT_GELU_TANH)
@@ -34,7 +34,8 @@ _DT = {torch.float32: F32, torch.bfloat16: BF16}
 EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b200seq_error_flags", "b200seq_embed_streams", "b200seq_hc_norm", "b200seq_hc_norm_conv",
            "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_linear_gated", "b200seq_attn_prep", "b200seq_attn", "b200seq_attn_scratch_floats",
            "b200seq_ssm_scan", "b200seq_ssm_scratch_floats", "b200seq_argmax", "b200seq_linear_act", "b200seq_act", "b200seq_depth_norm", "b200seq_attn_prep_ex",
-           "b200seq_attn_ex", "b200seq_moe_route", "b200seq_moe_sort", "b200seq_moe_linear", "b200seq_moe_gather", "b200seq_moe_combine", "b200seq_moe_router"]
+           "b200seq_attn_ex", "b200seq_moe_route", "b200seq_moe_sort", "b200seq_moe_linear", "b200seq_moe_gather", "b200seq_moe_combine", "b200seq_moe_router", "b200seq_moe_table_route",
+           "b200seq_latent_prep", "b200seq_rotary", "b200seq_retention", "b200seq_retention_scratch_floats", "b200seq_token_shift", "b200seq_post_norm"]
 
 
 class SeqError(RuntimeError):
@@ -53,19 +54,46 @@ class AttnDesc(C.Structure):
     """b200seq_attn_desc: sizes, columns of the projection row and mask / rotation constants of one attention layer"""
     _fields_ = [("H", C.c_int32), ("G", C.c_int32), ("D", C.c_int32), ("V", C.c_int32), ("q_col", C.c_int32), ("k_col", C.c_int32), ("v_col", C.c_int32),
                 ("gate_col", C.c_int32), ("scale", C.c_float), ("chunk", C.c_int32), ("window", C.c_int32), ("pool", C.c_int32), ("qk_eps", C.c_float),
-                ("rot_dims", C.c_int32), ("rot_freq", C.c_void_p), ("rot_scale", C.c_float)]
+                ("rot_dims", C.c_int32), ("rot_freq", C.c_void_p), ("rot_scale", C.c_float), ("sink", C.c_void_p), ("latent_v", C.c_int32), ("gate", C.c_void_p), ("gate_ld", C.c_int64)]
+
+
+class RetentionDesc(C.Structure):
+    """b200seq_retention_desc: sizes, columns of the projection row, decays and rotation constants of one retention layer"""
+    _fields_ = [("H", C.c_int32), ("D", C.c_int32), ("V", C.c_int32), ("q_col", C.c_int32), ("k_col", C.c_int32), ("v_col", C.c_int32), ("g_col", C.c_int32),
+                ("decay", C.c_void_p), ("eps", C.c_float), ("rot_dims", C.c_int32), ("rot_half", C.c_int32), ("rot_freq", C.c_void_p), ("rot_scale", C.c_float),
+                ("k_scale", C.c_float)]
+
+
+def retention_desc(H: int, D: int, V: int, decay: torch.Tensor, eps: float, k_scale: float, *, rot_freq: Optional[torch.Tensor] = None, rot_half: bool = True,
+                   rot_scale: float = 1.0) -> "RetentionDesc":
+    """descriptor for a projection row laid out q | k | v | gate; decay: device f32 [2, H] (decays, their base-2 logarithms); the caller
+    keeps decay and rot_freq alive"""
+    assert decay.dtype == torch.float32 and tuple(decay.shape) == (2, H) and decay.is_contiguous()
+    d = RetentionDesc(H, D, V, 0, H * D, 2 * H * D, 2 * H * D + H * V, decay.data_ptr(), eps, 2 * rot_freq.numel() if rot_freq is not None else 0, int(rot_half),
+                      rot_freq.data_ptr() if rot_freq is not None else None, rot_scale, k_scale)
+    d.width = 2 * H * D + 2 * H * V
+    return d
 
 
 def attn_desc(H: int, G: int, D: int, V: int, scale: float, *, values_from_keys: bool = False, gated: bool = True, chunk: int = 0, window: int = 0, pool: int = 0,
-              qk_eps: float = -1.0, rot_freq: Optional[torch.Tensor] = None, rot_scale: float = 1.0) -> "AttnDesc":
+              qk_eps: float = -1.0, rot_freq: Optional[torch.Tensor] = None, rot_scale: float = 1.0, sink: Optional[torch.Tensor] = None) -> "AttnDesc":
     """descriptor for a projection row laid out q | k | v | gate (v absent when the values are the keys, gate absent when not gated);
     rot_freq: device f32 [rot_dims / 2] (the caller keeps it alive)"""
     k_col = H * D
     v_col = k_col if values_from_keys else k_col + G * D
     end = v_col + (G * D if values_from_keys else G * V)
     d = AttnDesc(H, G, D, V, 0, k_col, v_col, end if gated else -1, scale, chunk, window, pool, qk_eps, 2 * rot_freq.numel() if rot_freq is not None else 0,
-                 rot_freq.data_ptr() if rot_freq is not None else None, rot_scale)
+                 rot_freq.data_ptr() if rot_freq is not None else None, rot_scale, sink.data_ptr() if sink is not None else None, 0)
     d.width = end + (H if gated else 0)
+    return d
+
+
+def latent_attn_desc(H: int, R: int, Rd: int, scale: float, *, gated: bool = True, sink: Optional[torch.Tensor] = None) -> "AttnDesc":
+    """descriptor of the attend step of a latent-attention layer: H query heads of size R + Rd (latent-space query | rotated part) in rows
+    [H * (R + Rd)] (gate logits: the `gate` argument of attn_ex) over ONE key head [c | kr] whose values are its first R floats; no rotation here (b200seq_latent_prep did it)"""
+    D = R + Rd
+    d = AttnDesc(H, 1, D, R, 0, 0, 0, 0 if gated else -1, scale, 0, 0, 0, -1.0, 0, None, 1.0, sink.data_ptr() if sink is not None else None, 1)
+    d.width = H * D
     return d
 
 
@@ -274,9 +302,14 @@ def attn_prep_ex(proj: torch.Tensor, step: "StepDesc", d: "AttnDesc", kpool: tor
 
 
 @_timed
-def attn_ex(proj: torch.Tensor, step: "StepDesc", d: "AttnDesc", kpool: torch.Tensor, vpool: torch.Tensor, out: torch.Tensor, scratch: Optional[torch.Tensor] = None,
-            kpooled: Optional[torch.Tensor] = None, vpooled: Optional[torch.Tensor] = None):
+def attn_ex(proj: torch.Tensor, step: "StepDesc", d: "AttnDesc", kpool: torch.Tensor, vpool: Optional[torch.Tensor], out: torch.Tensor,
+            scratch: Optional[torch.Tensor] = None, kpooled: Optional[torch.Tensor] = None, vpooled: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None):
+    """gate: f32 [T, H] view (row stride free) of the gate logits when they do not lie in the query rows (d.gate_col is then only a flag)"""
     _, _, ld = _rows2d(proj)
+    if gate is not None:        # the descriptor of a call is a copy: the layer's own stays as it was
+        d2 = AttnDesc.from_buffer_copy(d)
+        d2.gate, d2.gate_ld = gate.data_ptr(), gate.stride(0)
+        d = d2
     assert out.is_contiguous() and (scratch is None or (scratch.dtype == torch.float32 and scratch.is_contiguous()))
     _check(lib().b200seq_attn_ex(_p(proj), C.c_int64(ld), C.byref(step), C.byref(d), _p(kpool), _p(vpool), _p(kpooled), _p(vpooled), _p(out), _DT[out.dtype], _p(scratch),
                                  C.c_size_t(scratch.numel() if scratch is not None else 0), _st(proj)))
@@ -297,6 +330,13 @@ def moe_router(x: torch.Tensor, w: torch.Tensor, E: int, groups: int, keep: int,
     _, NR, ldz = _rows2d(z)
     assert w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape) == (NR, K) and z.dtype == torch.float32 and z.shape[0] == T
     _check(lib().b200seq_moe_router(_p(x), _DT[x.dtype], C.c_int64(ldx), _p(w), T, NR, K, E, groups, keep, top, _p(z), C.c_int64(ldz), _p(ids), _p(wts), _st(x)))
+
+
+@_timed
+def moe_table_route(table: torch.Tensor, tok_ids: torch.Tensor, T: int, E: int, top: int, ids: torch.Tensor, wts: torch.Tensor, counts: Optional[torch.Tensor]):
+    """ids[t][j] = table[tok_ids[t]][j], wts = 1 / top: the experts of a token are a row of a table indexed by its token id"""
+    assert table.dtype == torch.int32 and table.is_contiguous() and table.shape[1] == top and tok_ids.dtype == torch.int32 and ids.numel() >= T * top
+    _check(lib().b200seq_moe_table_route(_p(table), _p(tok_ids), T, E, top, _p(ids), _p(wts), _p(counts), _st(table)))
 
 
 @_timed
@@ -358,6 +398,61 @@ def attn(qkvg: torch.Tensor, step: "StepDesc", kpool: torch.Tensor, vpool: torch
     assert out.is_contiguous() and (scratch is None or (scratch.dtype == torch.float32 and scratch.is_contiguous()))
     _check(lib().b200seq_attn(_p(qkvg), C.c_int64(ld), C.byref(step), _p(kpool), _p(vpool), H, G, D, V, C.c_float(scale), chunk, window, int(gated),
                               _p(out), _DT[out.dtype], _p(scratch), C.c_size_t(scratch.numel() if scratch is not None else 0), _st(qkvg)))
+
+
+@_timed
+def latent_prep(proj: torch.Tensor, c_col: int, gate_col: int, q: torch.Tensor, step: "StepDesc", H: int, Dn: int, Rd: int, R: int, norm_w: torch.Tensor, eps: float,
+                rot_freq: Optional[torch.Tensor], rot_scale: float, kpool: torch.Tensor, Qp: torch.Tensor, qn: torch.Tensor):
+    _, _, ldp = _rows2d(proj)
+    _, _, ldq = _rows2d(q)
+    _, _, ldQ = _rows2d(Qp)
+    assert qn.is_contiguous() and kpool.is_contiguous() and kpool.shape[-1] == R + Rd
+    _check(lib().b200seq_latent_prep(_p(proj), C.c_int64(ldp), c_col, gate_col, _p(q), C.c_int64(ldq), C.byref(step), H, Dn, Rd, R, _p(norm_w), C.c_float(eps),
+                                     _p(rot_freq), C.c_float(rot_scale), _p(kpool), _p(Qp), C.c_int64(ldQ), _p(qn), _DT[qn.dtype], _st(proj)))
+
+
+@_timed
+def rotary(x: torch.Tensor, col: int, nheads: int, D: int, step: "StepDesc", rot_freq: Optional[torch.Tensor], half: bool, rot_scale: float = 1.0, mult: float = 1.0):
+    _, _, ld = _rows2d(x)
+    _check(lib().b200seq_rotary(_p(x), C.c_int64(ld), col, nheads, D, C.byref(step), 2 * rot_freq.numel() if rot_freq is not None else 0, int(half), _p(rot_freq),
+                                C.c_float(rot_scale), C.c_float(mult), _st(x)))
+
+
+def retention_scratch_floats(T: int, B: int, H: int, D: int, V: int) -> int:
+    """floats of work area a retention step of T tokens in B entries wants (0: every entry brings one token)"""
+    f = lib().b200seq_retention_scratch_floats
+    f.restype = C.c_size_t
+    return int(f(T, B, H, D, V))
+
+
+@_timed
+def retention(proj: torch.Tensor, step: "StepDesc", d: "RetentionDesc", state: torch.Tensor, out: torch.Tensor, scratch: Optional[torch.Tensor] = None):
+    _, _, ld = _rows2d(proj)
+    assert out.is_contiguous() and state.is_contiguous() and (scratch is None or (scratch.dtype == torch.float32 and scratch.is_contiguous()))
+    _check(lib().b200seq_retention(_p(proj), C.c_int64(ld), C.byref(step), C.byref(d), _p(state), _p(out), _DT[out.dtype], _p(scratch),
+                                   C.c_size_t(scratch.numel() if scratch is not None else 0), _st(proj)))
+
+
+@_timed
+def token_shift(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, step: "StepDesc", out_plain: Optional[torch.Tensor], out_shift: torch.Tensor):
+    T, W = x.shape
+    assert x.is_contiguous() and out_shift.is_contiguous() and (out_plain is None or (out_plain.is_contiguous() and out_plain.dtype == out_shift.dtype))
+    _check(lib().b200seq_token_shift(_p(x), W, _p(mu), _p(state), C.byref(step), _p(out_plain), _p(out_shift), _DT[out_shift.dtype], _st(x)))
+
+
+@_timed
+def post_norm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float, *, y: Optional[torch.Tensor] = None, zg: Optional[torch.Tensor] = None,
+              gate_b: Optional[torch.Tensor] = None, alpha: float = 1.0, rows: Optional[torch.Tensor] = None, x_out: Optional[torch.Tensor] = None,
+              a_out: Optional[torch.Tensor] = None, state_out: Optional[torch.Tensor] = None, next_mu: Optional[torch.Tensor] = None,
+              next_state: Optional[torch.Tensor] = None, a_shift_out: Optional[torch.Tensor] = None, step: Optional["StepDesc"] = None):
+    """layer norm (weight, bias) after the gated residual sum: LN(alpha * x + sigmoid(zg + gate_b) * y); see include/b200seq.h"""
+    W = x.shape[-1]
+    R = x.shape[0] if rows is None else rows.numel()
+    o = a_out if a_out is not None else a_shift_out
+    assert x.is_contiguous() and (y is None or y.is_contiguous())
+    _check(lib().b200seq_post_norm(_p(x), _p(y), _p(zg), C.c_int64(zg.stride(0) if zg is not None else 0), _p(gate_b), C.c_float(alpha), _p(w), _p(b), C.c_float(eps), W,
+                                   _p(rows), R, _p(x_out), _p(a_out), _DT[o.dtype] if o is not None else F32, _p(state_out), _p(next_mu), _p(next_state), _p(a_shift_out),
+                                   C.byref(step) if step is not None else None, _st(x)))
 
 
 def ssm_scratch_floats(T: int, B: int, H: int, V: int, N: int) -> int:

@@ -64,7 +64,7 @@ typedef struct b200seq_step {
 const char* b200seq_last_error(void);
 int b200seq_version(void);
 int64_t b200seq_launch_count(void);
-/* bit 0: a KV position fell outside its block table; bit 1: a bounded wait of the tensor-core GEMM ran out */
+/* bit 0: a KV position fell outside its block table; bit 1: a bounded wait of the tensor-core GEMM ran out; bit 2: an expert table entry outside the experts */
 int b200seq_error_flags(int* flags_out);
 
 /* X[t][s][:] = table[ids[t]][:] * scale for every stream s.  table: bf16 [V, W]; X: f32 [T, S, W]. */
@@ -138,6 +138,7 @@ int b200seq_ssm_scan(const float* proj, int64_t ldp, int z0, int dt0, const floa
 #define B200SEQ_ACT_SWISH_CLAMP 0
 #define B200SEQ_ACT_GELU_TANH 1
 #define B200SEQ_ACT_RELU2 2
+#define B200SEQ_ACT_IDENT 3 /* plain kind: the product itself, written in out_dtype (a projection whose result feeds the next linear layer) */
 
 /* out = act(x . w^T), the product itself never reaches memory.  w: bf16 [N, K]; out [M, N / 2] (gated kinds) or [M, N] (plain kinds) in
  * out_dtype, row stride ldo.  M <= 8: weight-streaming rows (f32 or bf16 activations); more rows: the tensor-core path, which needs bf16
@@ -180,11 +181,70 @@ typedef struct b200seq_attn_desc {
     int32_t rot_dims;
     const float* rot_freq;
     float rot_scale;
+    const float* sink;  /* attend: device f32 [H] or null; exp(sink[h]) is one more term of head h's soft-max denominator (no key, no value, not scaled) */
+    int32_t latent_v;   /* attend: 1 = the values are the first V floats of the (single) key head's pool rows, vpool is not read (G == 1, V <= D) */
+    const float* gate;  /* attend: when not null (and gate_col >= 0) the gate logit of (t, h) is gate[t * gate_ld + h] instead of the query row's */
+    int64_t gate_ld;
 } b200seq_attn_desc;
 int b200seq_attn_prep_ex(float* proj, int64_t ld, const b200seq_step* st, const b200seq_attn_desc* d, float* kpool, float* vpool, float* kpooled, float* vpooled,
                          void* stream);
 int b200seq_attn_ex(const float* proj, int64_t ld, const b200seq_step* st, const b200seq_attn_desc* d, const float* kpool, const float* vpool,
                     const float* kpooled, const float* vpooled, void* out, int out_dtype, float* scratch, size_t scratch_floats, void* stream);
+
+/* ---- latent attention: prep ---------------------------------------------------------------------------------------------------------------
+ * The cache of a latent-attention layer holds per token one row [c (R) | kr (Rd)] of a pool [blocks][block_size][R + Rd]: the normed latent
+ * c = rms_norm(kv[0 .. R), eps) * norm_w and the rotated key part kr = rot(kv[R .. R + Rd)) that all heads share, kv = proj[t][c_col ..).
+ * Keys never leave the latent space: with k_h = [W_h c | kr] the score of head h is (W_h^T q_h[0 .. Dn)) . c + rot(q_h[Dn ..)) . kr, so the
+ * attention runs as H query heads of size R + Rd over one key head whose values are its first R floats (b200seq_attn_desc.latent_v), and
+ * the value projection is applied to the R-sized result.  This call, per token: writes the pool row; writes rot(q_h[Dn ..)) to
+ * Qp[t][h * (R + Rd) + R ..) (the caller's projection fills the R columns before it); writes q_h[0 .. Dn) in qn_dtype to qn[(t * H + h)][Dn]
+ * (the input of that projection); copies the H gate logits proj[t][gate_col ..) to Qp[t][H * (R + Rd) ..) when gate_col >= 0.
+ * q: f32 [T, ldq] = H heads of [Dn | Rd].  Rotation: pairs (2i, 2i + 1), angle pos * rot_freq[i], cos and sin times rot_scale. */
+int b200seq_latent_prep(const float* proj, int64_t ldp, int c_col, int gate_col, const float* q, int64_t ldq, const b200seq_step* st, int H, int Dn, int Rd, int R,
+                        const float* norm_w, float eps, const float* rot_freq, float rot_scale, float* kpool, float* Qp, int64_t ldQ, void* qn, int qn_dtype,
+                        void* stream);
+
+/* ---- rotary positions on head vectors inside projection rows -------------------------------------------------------------------------------
+ * x[t][col + h * D + ..], h < nheads: the first rot_dims dimensions of every head turn by pos * freq[i]; pair (i, i + rot_dims / 2) when
+ * half = 1, (2i, 2i + 1) when half = 0; cos and sin times rot_scale; then every element of the head times mult.  In place. */
+int b200seq_rotary(float* x, int64_t ld, int col, int nheads, int D, const b200seq_step* st, int rot_dims, int half, const float* freq, float rot_scale, float mult,
+                   void* stream);
+
+/* ---- retention ---------------------------------------------------------------------------------------------------------------------------------
+ * Linear attention with one fixed decay per head, no soft-max, no denominator.  Columns of the f32 projection row: q at q_col (H*D),
+ * k at k_col (H*D), v at v_col (H*V), gate at g_col (H*V).  q and k get rotary positions (as b200seq_rotary; q and k are turned in place
+ * in steps of portions), k is multiplied by k_scale; per head with state[slot][H][D][V] (f32, read as zero when ent_pos0 == 0):
+ *   S_t = decay[h] * S_(t-1) + k_t v_t^T;   o_t = S_t^T q_t;   out[t][h] = o_t / sqrt(mean(o_t^2) + eps) * silu(gate_t[h])   (act dtype [T, H*V])
+ * decay: device f32 [2][H] = the decays, then their base-2 logarithms.  Steps in which every entry brings one token run one kernel and need
+ * no work area; other steps cut the portions into chunks that run in parallel and need b200seq_retention_scratch_floats(...) floats. */
+typedef struct b200seq_retention_desc {
+    int32_t H, D, V;
+    int32_t q_col, k_col, v_col, g_col;
+    const float* decay;
+    float eps;
+    int32_t rot_dims, rot_half;
+    const float* rot_freq;
+    float rot_scale, k_scale;
+} b200seq_retention_desc;
+size_t b200seq_retention_scratch_floats(int T, int B, int H, int D, int V);
+int b200seq_retention(float* proj, int64_t ld, const b200seq_step* st, const b200seq_retention_desc* d, float* state, void* out, int out_dtype, float* scratch,
+                      size_t scratch_floats, void* stream);
+
+/* ---- post-norm residual path with token shift and gated residual ------------------------------------------------------------------------
+ * token_shift: out_shift[t] = x[t] + (prev - x[t]) * mu with prev = x[t - 1] inside a portion, state[slot] for a portion's first token
+ * (zero when ent_pos0 == 0); out_plain[t] = x[t] (optional); both [T, W] in out_dtype.  The state is only read here.
+ * post_norm, one block per row r (token t = rows ? rows[r] : r):
+ *   v = y ? alpha * x[t] + (zg ? sigmoid(zg[t * ldz + i] + gate_b[i]) : 1) * y[t] : x[t]
+ *   n = (v - mean) / sqrt(var + eps) * w + b          (biased variance; b may be null)
+ *   x_out[t] <- n (f32, optional, may be x);  a_out[r] <- n in out_dtype (optional)
+ *   state_out (optional, all rows): state_out[slot] <- x[t] for the last token of every entry (the shift state of the layer whose mixer read x)
+ *   next_mu (optional, steps with one token per entry): a_shift_out[r] <- n + (prev - n) * next_mu, prev = next_state[slot] or zero: the
+ *   token shift of the next mixer in the same pass. */
+int b200seq_token_shift(const float* x, int W, const float* mu, const float* state, const b200seq_step* st, void* out_plain, void* out_shift, int out_dtype,
+                        void* stream);
+int b200seq_post_norm(const float* x, const float* y, const float* zg, int64_t ldz, const float* gate_b, float alpha, const float* w, const float* b, float eps, int W,
+                      const int32_t* rows, int R, float* x_out, void* a_out, int out_dtype, float* state_out, const float* next_mu, const float* next_state,
+                      void* a_shift_out, const b200seq_step* st, void* stream);
 
 /* ---- mixture of experts -------------------------------------------------------------------------------------------------------------------
  * route: z f32 [T, >= E] (stride ldz) router logits; s = sigmoid(z).  Experts form `groups` equal groups of neighbours; a group's score is
@@ -197,6 +257,9 @@ int b200seq_moe_route(const float* z, int64_t ldz, int T, int E, int groups, int
  * weight (bf16 [NR, K]; rows behind the E experts' are projected and left in z for the caller), then the choice of b200seq_moe_route on z[t][0..E). */
 int b200seq_moe_router(const void* x, int x_dtype, int64_t ldx, const void* w_bf16, int T, int NR, int K, int E, int groups, int keep, int top, float* z, int64_t ldz,
                        int32_t* ids, float* wts, void* stream);
+/* Choice by table instead of a router: ids[t][j] = table[tok_ids[t]][j] (table int32 [vocab][top], the entries of a row differ),
+ * wts[t][j] = 1 / top; counts as above (optional). */
+int b200seq_moe_table_route(const int32_t* table, const int32_t* tok_ids, int T, int E, int top, int32_t* ids, float* wts, int32_t* counts, void* stream);
 int b200seq_moe_sort(const int32_t* ids, int pairs, int E, const int32_t* counts, int32_t* offs, int32_t* sorted, int32_t* slot_of, void* stream);
 /* One projection of every pair through its expert's weight: w bf16 [E][N][K].  Row r of the result belongs to pair p = sorted ? sorted[r] : r
  * (sorted + offs from b200seq_moe_sort: tiles of one expert's rows; null: one launch row per pair, weights streamed, for few pairs).
