@@ -178,3 +178,75 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], layers_out
             layers_out.append(x.clone())
     x = layer_norm(x, w["final.norm"], w["final.norm.b"], eps)
     return x @ w["embed"].T
+
+
+# ---- random models and checkpoints (test fixtures) -------------------------------------------------------------------------------------
+def random_model(cfg: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """random bfloat16-representable weights with the checkpoint's names and shapes; layers with weights_of get none"""
+    g = torch.Generator().manual_seed(seed)
+    W, V = cfg["width"], cfg["vocab"]
+    r = lambda *s, sc=1.0: (torch.randn(*s, generator=g) * sc).bfloat16().float()
+    P = {"embed": r(V, W, sc=1.0), "final.norm": 1 + r(W, sc=0.1), "final.norm.b": r(W, sc=0.1)}
+    for i, lay in enumerate(cfg["layers"]):
+        if lay.get("weights_of") is not None:
+            continue
+        m, p = lay["mixer"], f"l{i}."
+        subs = ("1", "2") if lay.get("mlp") else ("1",)
+        for q in subs:
+            P[p + "norm" + q], P[p + "norm" + q + ".b"] = 1 + r(W, sc=0.1), r(W, sc=0.1)
+            P[p + "rg" + q], P[p + "rg" + q + ".b"] = r(W, W, sc=W ** -0.5), r(W, sc=0.5)
+        P[p + "shift"] = torch.rand(W, generator=g).bfloat16().float()
+        H = m["heads"]
+        if lay["type"] == "retention":
+            D, Vd = m["dim"], m["vdim"]
+            P[p + "mix.q"], P[p + "mix.k"] = r(H * D, W, sc=2.0 * W ** -0.5), r(H * D, W, sc=2.0 * W ** -0.5)
+            P[p + "mix.v"], P[p + "mix.g"] = r(H * Vd, W, sc=W ** -0.5), r(H * Vd, W, sc=W ** -0.5)
+            P[p + "mix.o"] = r(W, H * Vd, sc=2.0 * (H * Vd) ** -0.5)
+        else:
+            D, Rd, Vd, R, Rq = m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            P[p + "mix.dq"], P[p + "mix.dq.norm"] = r(Rq, W, sc=W ** -0.5), 1 + r(Rq, sc=0.1)
+            P[p + "mix.uq"] = r(H * (D + Rd), Rq, sc=2.0 * Rq ** -0.5)
+            P[p + "mix.dkv"], P[p + "mix.dkv.norm"] = r(R + Rd, W, sc=W ** -0.5), 1 + r(R, sc=0.1)
+            P[p + "mix.uk"], P[p + "mix.uv"] = r(H * D, R, sc=2.0 * R ** -0.5), r(H * Vd, R, sc=R ** -0.5)
+            P[p + "mix.sink"] = r(H, sc=1.5)
+            P[p + "mix.g"] = r(H, W, sc=W ** -0.5)
+            P[p + "mix.o"] = r(W, H * Vd, sc=2.0 * (H * Vd) ** -0.5)
+        mlp = lay.get("mlp")
+        if mlp:
+            E, top, ff = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+            for e in range(E):
+                P[p + f"mlp.e{e}.gate"], P[p + f"mlp.e{e}.up"] = r(ff, W, sc=2.0 * W ** -0.5), r(ff, W, sc=2.0 * W ** -0.5)
+                P[p + f"mlp.e{e}.down"] = r(W, ff, sc=2.0 * ff ** -0.5)
+            P[p + "mlp.table"] = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(V)]).to(torch.int32)
+            if mlp.get("shared"):
+                sf = mlp["shared"]["ff"]
+                P[p + "mlp.shared.gate"], P[p + "mlp.shared.up"] = r(sf, W, sc=2.0 * W ** -0.5), r(sf, W, sc=2.0 * W ** -0.5)
+                P[p + "mlp.shared.down"] = r(W, sf, sc=2.0 * sf ** -0.5)
+    return {k: (v.bfloat16().float() if v.is_floating_point() else v) for k, v in P.items()}      # the checkpoint holds bfloat16: what is not representable is rounded here
+
+
+def write_checkpoint(folder: str, cfg: dict, P: Dict[str, torch.Tensor]) -> None:
+    """config.json + model.safetensors (bfloat16, integer tables int32), written with the file format's own rules"""
+    import json
+    import os
+    import struct
+
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    head, blobs, off = {}, [], 0
+    for k, v in P.items():
+        if v.is_floating_point():
+            b, dt = v.bfloat16().contiguous().view(torch.uint8).numpy().tobytes(), "BF16"
+        else:
+            b, dt = v.to(torch.int32).contiguous().numpy().tobytes(), "I32"
+        head[k] = {"dtype": dt, "shape": list(v.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    hj = json.dumps(head).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
