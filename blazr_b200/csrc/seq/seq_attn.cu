@@ -203,6 +203,17 @@ __global__ void latent_prep_kernel(const LatentPrep a, const b200seq_step st, in
         }
     }
     const float* qr = a.q + (int64_t)t * a.ldq;
+    if (!a.Qp) {   // the step attends over per-head keys: the rotated part of every query head turns in place, nothing else is needed
+        float* qw = const_cast<float*>(qr);
+        for (int idx = tid; idx < H * np; idx += blockDim.x) {
+            const int h = idx / np, i = idx - h * np;
+            float* p = qw + (int64_t)h * (Dn + Rd) + Dn + 2 * i;
+            const float u = p[0], v = p[1];
+            p[0] = u * cs[i] - v * cs[np + i];
+            p[1] = v * cs[i] + u * cs[np + i];
+        }
+        return;
+    }
     float* Qt = a.Qp + (int64_t)t * a.ldQ;
     for (int idx = tid; idx < H * np; idx += blockDim.x) {
         const int h = idx / np, i = idx - h * np;
@@ -216,6 +227,24 @@ __global__ void latent_prep_kernel(const LatentPrep a, const b200seq_step st, in
     }
     if (a.gate_col >= 0)
         for (int h = tid; h < H; h += blockDim.x) Qt[(int64_t)H * (R + Rd) + h] = a.proj[(int64_t)t * a.ldp + a.gate_col + h];
+}
+
+// grid (rows of the gathered context): row r = the r-th (entry, position) pair, entries in order, positions 0 .. pos0 + len - 1 of each;
+// copies the first R floats of the position's pool row (the latent) in the activation type
+__global__ void latent_gather_kernel(const float* __restrict__ kpool, int64_t kld, const b200seq_step st, int R, void* __restrict__ out, int out_dtype, int* err) {
+    int64_t r = blockIdx.x;
+    int e = 0;
+    for (; e < st.B; ++e) {
+        const int n = st.ent_pos0[e] + st.ent_start[e + 1] - st.ent_start[e];
+        if (r < n) break;
+        r -= n;
+    }
+    if (e == st.B) return;
+    const int pos = (int)r;
+    const int64_t row = kv_row(st, e, pos, err);
+    if (row < 0) return;
+    const float* src = kpool + row * kld;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) store_act(out, out_dtype, (int64_t)blockIdx.x * R + i, src[i]);
 }
 
 // ---- attend -----------------------------------------------------------------------------------------------------------------------
@@ -247,6 +276,10 @@ struct AttnArgs {
     const float* gate;   // gate logits [T][gld] (+ h)
     int64_t gld;
     int64_t kld, vld;    // floats per position in kpool / vpool (G * D and G * V, or the key row's width when the values lie inside the key rows)
+    int ctx_rows;        // 1: kpool / vpool rows are the step's gathered context, entry after entry, position after position (no pages)
+    int kd;              // floats of a key head that lie in kpool (at g * kd); the remaining D - kd come from krot, one part for all heads
+    const float* krot;   // paged rows of krld floats (pointer already at the part's first column), or null
+    int64_t krld;
 };
 
 __device__ __forceinline__ bool attn_find_tile(const b200seq_step& st, int idx, int QT, int& e, int& t0, int& nq) {
@@ -297,6 +330,9 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
     }
     int kbeg = a.chunk > 0 ? (p0 / a.chunk) * a.chunk : 0;
     if (a.window > 0) kbeg = max(kbeg, p0 - a.window + 1);
+    int64_t cstart = 0;   // first row of this entry's context in the gathered form: the contexts of the entries before it
+    if (a.ctx_rows)
+        for (int i = 0; i < e; ++i) cstart += st.ent_pos0[i] + st.ent_start[i + 1] - st.ent_start[i];
     // queries (zero rows where the tile has no token or the block no head)
     for (int idx = tid; idx < RQ * Dp; idx += AT_NT) {
         const int r = idx / Dp, d = idx - r * Dp;
@@ -323,7 +359,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
 #pragma unroll
         for (int j = 0; j < VPT; ++j) acc[i][j] = 0.f;
     }
-    const bool vecD = ((D | a.kld) & 3) == 0, vecV = ((V | a.vld) & 3) == 0;
+    const bool vecD = ((D | a.kld | a.kd | a.krld) & 3) == 0 && (reinterpret_cast<uintptr_t>(a.krot) & 15) == 0, vecV = ((V | a.vld) & 3) == 0;
     // pooled blocks every row of the tile may see (the tile's last row sees the most), then the positions from kbeg to hi
     const int nbmax = (a.pool > 0 && hi - a.window + 1 > 0) ? (hi - a.window + 1) / a.pool : 0;
     const int npt = (nbmax + AT_KT - 1) / AT_KT;
@@ -334,7 +370,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
         const bool in = pooled ? kp < nbmax : kp <= hi;
         const float* src = !in ? nullptr
                            : pooled ? a.vpp + (pooled_row(bt, bs, a.pool, a.ppp, kp) * G + g) * V
-                                    : a.vpool + ((int64_t)bt[kp / bs] * bs + kp % bs) * a.vld + (int64_t)g * V;
+                                    : a.vpool + (a.ctx_rows ? cstart + kp : (int64_t)bt[kp / bs] * bs + kp % bs) * a.vld + (int64_t)g * V;
         if (vecV) {
             for (int c4 = sub; c4 < (VS >> 2); c4 += 4)
                 *reinterpret_cast<float4*>(Vs + k * VS + 4 * c4) = (in && 4 * c4 < V) ? *reinterpret_cast<const float4*>(src + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -351,14 +387,17 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
             const int k = tid >> 2, sub = tid & 3;
             const int kp = k0 + k;
             const bool in = pooled ? kp < nbmax : kp <= hi;
+            const int64_t prow = (in && !pooled) ? (int64_t)bt[kp / bs] * bs + kp % bs : 0;
             const float* src = !in ? nullptr
                                : pooled ? a.kpp + (pooled_row(bt, bs, a.pool, a.ppp, kp) * G + g) * D
-                                        : a.kpool + ((int64_t)bt[kp / bs] * bs + kp % bs) * a.kld + (int64_t)g * D;
+                                        : a.kpool + (a.ctx_rows ? cstart + kp : prow) * a.kld + (int64_t)g * a.kd;
+            const float* src2 = (in && a.krot) ? a.krot + prow * a.krld - a.kd : src;   // dimensions kd .. D - 1 of the key, indexed by d
+            const int kd = pooled ? D : a.kd;
             if (vecD) {
                 for (int d4 = sub; d4 < (D >> 2); d4 += 4)
-                    *reinterpret_cast<float4*>(Ks + k * QS + 4 * d4) = in ? *reinterpret_cast<const float4*>(src + 4 * d4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    *reinterpret_cast<float4*>(Ks + k * QS + 4 * d4) = in ? *reinterpret_cast<const float4*>((4 * d4 < kd ? src : src2) + 4 * d4) : make_float4(0.f, 0.f, 0.f, 0.f);
             } else {
-                for (int d = sub; d < Dp; d += 4) Ks[k * QS + d] = (in && d < D) ? src[d] : 0.f;
+                for (int d = sub; d < Dp; d += 4) Ks[k * QS + d] = (in && d < D) ? (d < kd ? src[d] : src2[d]) : 0.f;
             }
         }
         if (!a.share_kv) load_v(k0, pooled);
@@ -531,6 +570,9 @@ static int desc_check(const b200seq_attn_desc* d, const char* what) {
         return fail(B200SEQ_ERR_INVALID_ARG, "%s: bad head counts, sizes or columns", what);
     if (!d->latent_v && d->v_col == d->k_col && d->V != d->D) return fail(B200SEQ_ERR_INVALID_ARG, "%s: values taken from the keys need V == D", what);
     if (d->latent_v && (d->G != 1 || d->V > d->D)) return fail(B200SEQ_ERR_INVALID_ARG, "%s: values inside the key rows need one key head and V <= D", what);
+    if (d->kd < 0 || d->kd > d->D || ((d->kd > 0 && d->kd < d->D) != (d->krot != nullptr)) || (d->krot && (d->pool > 0 || d->krot_ld < d->D - d->kd)))
+        return fail(B200SEQ_ERR_INVALID_ARG, "%s: a key part shared by all heads needs its rows, 0 < kd < D and no pooled blocks", what);
+    if (d->ctx_rows && (d->pool > 0 || d->latent_v)) return fail(B200SEQ_ERR_INVALID_ARG, "%s: gathered context rows go with plain key / value rows", what);
     if (d->rot_dims < 0 || d->rot_dims > d->D || (d->rot_dims & 1) || (d->rot_dims > 0 && !d->rot_freq))
         return fail(B200SEQ_ERR_INVALID_ARG, "%s: rotary dimensions must be even, at most D, with a frequency table", what);
     if (d->pool < 0 || (d->pool > 0 && d->window < 1)) return fail(B200SEQ_ERR_INVALID_ARG, "%s: pooled blocks need a window", what);
@@ -559,21 +601,30 @@ int b200seq_attn_prep_ex(float* proj, int64_t ld, const b200seq_step* st, const 
 }
 
 int b200seq_attn_prep(float* qkvg, int64_t ld, const b200seq_step* st, float* kpool, float* vpool, int H, int G, int D, int V, float qk_eps, void* stream) {
-    const b200seq_attn_desc d{H, G, D, V, 0, H * D, (H + G) * D, -1, 1.f, 0, 0, 0, qk_eps, 0, nullptr, 1.f, nullptr, 0, nullptr, 0};
+    const b200seq_attn_desc d{H, G, D, V, 0, H * D, (H + G) * D, -1, 1.f, 0, 0, 0, qk_eps, 0, nullptr, 1.f, nullptr, 0, nullptr, 0, 0, 0, 0, nullptr, 0};
     return b200seq_attn_prep_ex(qkvg, ld, st, &d, kpool, vpool, nullptr, nullptr, stream);
 }
 
 int b200seq_latent_prep(const float* proj, int64_t ldp, int c_col, int gate_col, const float* q, int64_t ldq, const b200seq_step* st, int H, int Dn, int Rd, int R,
                         const float* norm_w, float eps, const float* rot_freq, float rot_scale, float* kpool, float* Qp, int64_t ldQ, void* qn, int qn_dtype,
                         void* stream) {
-    if (!proj || !q || !st || !norm_w || !kpool || !Qp || !qn || H < 1 || Dn < 1 || Rd < 0 || (Rd & 1) || R < 1 || c_col < 0 || (Rd > 0 && !rot_freq))
+    if (!proj || !q || !st || !norm_w || !kpool || ((Qp == nullptr) != (qn == nullptr)) || H < 1 || Dn < 1 || Rd < 0 || (Rd & 1) || R < 1 || c_col < 0 || (Rd > 0 && !rot_freq))
         return fail(B200SEQ_ERR_INVALID_ARG, "latent_prep: bad arguments (the rotated part has an even size)");
-    if (ldq < (int64_t)H * (Dn + Rd) || ldQ < (int64_t)H * (R + Rd) + (gate_col >= 0 ? H : 0)) return fail(B200SEQ_ERR_INVALID_ARG, "latent_prep: rows too short");
-    if (qn_dtype != B200SEQ_F32 && qn_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "latent_prep: activation dtype");
+    if (ldq < (int64_t)H * (Dn + Rd) || (Qp && ldQ < (int64_t)H * (R + Rd) + (gate_col >= 0 ? H : 0))) return fail(B200SEQ_ERR_INVALID_ARG, "latent_prep: rows too short");
+    if (Qp && qn_dtype != B200SEQ_F32 && qn_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "latent_prep: activation dtype");
     if (st->T == 0) return 0;
     const LatentPrep a{proj, ldp, c_col, gate_col, q, ldq, H, Dn, Rd, R, norm_w, eps, rot_freq, rot_scale, kpool, Qp, ldQ, qn, qn_dtype};
     latent_prep_kernel<<<st->T, 256, (size_t)(Rd + 40) * sizeof(float), (cudaStream_t)stream>>>(a, *st, error_flag_dev());
     SEQ_LAUNCH_CHECK("latent_prep");
+    return 0;
+}
+
+int b200seq_latent_gather(const float* kpool, int64_t kld, const b200seq_step* st, int R, int ctx_rows, void* out, int out_dtype, void* stream) {
+    if (!kpool || !st || !out || R < 1 || kld < R || ctx_rows < 0) return fail(B200SEQ_ERR_INVALID_ARG, "latent_gather: bad arguments");
+    if (out_dtype != B200SEQ_F32 && out_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "latent_gather: output dtype");
+    if (ctx_rows == 0) return 0;
+    latent_gather_kernel<<<ctx_rows, R >= 256 ? 128 : 64, 0, (cudaStream_t)stream>>>(kpool, kld, *st, R, out, out_dtype, error_flag_dev());
+    SEQ_LAUNCH_CHECK("latent_gather");
     return 0;
 }
 
@@ -604,7 +655,8 @@ int b200seq_attn_ex(const float* qkvg, int64_t ld, const b200seq_step* st, const
     if (p.nsplit > 1 && (!scratch || scratch_floats < (size_t)st->T * H * p.nsplit * (V + 2))) p.nsplit = 1;
     const int ppp = d->pool > 0 ? (st->block_size + d->pool - 1) / d->pool : 0;
     AttnArgs a{qkvg, ld, kpool, vpool, kpooled, vpooled, d->pool, ppp, d->q_col, d->gate_col, H, G, D, V, p.Rb, p.HB, p.QT, p.nsplit, 0, d->scale, d->chunk, d->window,
-               gated, out, out_dtype, scratch, error_flag_dev(), d->sink, d->gate ? d->gate : qkvg + (gated ? d->gate_col : 0), d->gate ? d->gate_ld : ld, (int64_t)G * D, d->latent_v ? (int64_t)G * D : (int64_t)G * V};
+               gated, out, out_dtype, scratch, error_flag_dev(), d->sink, d->gate ? d->gate : qkvg + (gated ? d->gate_col : 0), d->gate ? d->gate_ld : ld, d->kv_ld > 0 ? d->kv_ld : (int64_t)G * D,
+               d->kv_ld > 0 ? d->kv_ld : (d->latent_v ? (int64_t)G * D : (int64_t)G * V), d->ctx_rows, (d->kd > 0 && d->kd < D) ? d->kd : D, d->krot, d->krot_ld};
     if (d->latent_v) a.vpool = kpool;
     const int VPT = V <= 64 ? 4 : (V <= 128 ? 8 : 16);
     const int RQ = 16 * p.RT, QS = ((D + 3) & ~3) + 4;
@@ -648,7 +700,7 @@ int b200seq_attn_ex(const float* qkvg, int64_t ld, const b200seq_step* st, const
 
 int b200seq_attn(const float* qkvg, int64_t ld, const b200seq_step* st, const float* kpool, const float* vpool, int H, int G, int D, int V, float scale,
                  int chunk, int window, int gated, void* out, int out_dtype, float* scratch, size_t scratch_floats, void* stream) {
-    const b200seq_attn_desc d{H, G, D, V, 0, H * D, (H + G) * D, gated ? (H + G) * D + G * V : -1, scale, chunk, window, 0, -1.f, 0, nullptr, 1.f, nullptr, 0, nullptr, 0};
+    const b200seq_attn_desc d{H, G, D, V, 0, H * D, (H + G) * D, gated ? (H + G) * D + G * V : -1, scale, chunk, window, 0, -1.f, 0, nullptr, 1.f, nullptr, 0, nullptr, 0, 0, 0, 0, nullptr, 0};
     return b200seq_attn_ex(qkvg, ld, st, &d, kpool, vpool, nullptr, nullptr, out, out_dtype, scratch, scratch_floats, stream);
 }
 

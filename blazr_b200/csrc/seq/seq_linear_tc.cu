@@ -101,6 +101,8 @@ struct TcParams {
     int* err;
     const int32_t* offs;   // grouped form: [E + 1] first row of every group; rows of group e use the weight rows e * N .. e * N + N - 1
     int E;
+    int heads;             // per-head form (blockIdx.z = head e): every row goes through every head's weight rows e * N .., reading the columns
+    int64_t ocol;          // e * K .. of its x row and writing the columns e * ocol .. of its output row
 };
 constexpr int EPI_NONE = 0, EPI_GATED = 1, EPI_PLAIN_ACT = 2;
 
@@ -114,7 +116,9 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
     // token tiles vary fastest: the CTAs that run together share a few weight tiles and all activation tiles, which L2 holds, so the
     // weights cross HBM once instead of once per token tile
     const int n0 = blockIdx.y * BN;
-    int m0 = blockIdx.x * BM, m_end = p.M, wrow0 = n0;
+    int m0 = blockIdx.x * BM, m_end = p.M, wrow0 = n0, xk0 = 0;
+    int64_t oc0 = 0;
+    if (p.heads) wrow0 = (int)blockIdx.z * p.N + n0, xk0 = (int)blockIdx.z * p.K, oc0 = (int64_t)blockIdx.z * p.ocol;
     if (p.offs) {   // grouped: blockIdx.x counts the row tiles of all groups in group order; a tile never crosses into the next group's rows
         __shared__ int grp[3];
         if (threadIdx.x == 0) {
@@ -159,7 +163,7 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
             mbar_expect_tx(&full[s], STAGE_BYTES);
             uint8_t* st = smem + (size_t)s * STAGE_BYTES;
             tma_load_2d(st, &map_w, kb * BK, wrow0, &full[s]);
-            tma_load_2d(st + BN * BK * 2, &map_x, kb * BK, m0, &full[s]);
+            tma_load_2d(st + BN * BK * 2, &map_x, xk0 + kb * BK, m0, &full[s]);
         }
         if (*ab) {   // leave only when the copies already issued have landed (or the bounded wait gives up on them too)
             for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
@@ -198,13 +202,13 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
                 if (n < p.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (m0 + c + j < m_end) p.y[(int64_t)(m0 + c + j) * p.ldy + n] = __uint_as_float(r[j]);
+                        if (m0 + c + j < m_end) p.y[(int64_t)(m0 + c + j) * p.ldy + oc0 + n] = __uint_as_float(r[j]);
                 }
             } else if (p.epi == EPI_PLAIN_ACT) {
                 if (n < p.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (m0 + c + j < m_end) store_act(p.act_out, p.out_dtype, (int64_t)(m0 + c + j) * p.ldo + n, act_plain(p.act.kind, __uint_as_float(r[j])));
+                        if (m0 + c + j < m_end) store_act(p.act_out, p.out_dtype, (int64_t)(m0 + c + j) * p.ldo + oc0 + n, act_plain(p.act.kind, __uint_as_float(r[j])));
                 }
             } else {
 #pragma unroll
@@ -212,7 +216,7 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
                     const float mine = __uint_as_float(r[j]);
                     const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
                     if ((lane & 1) == 0 && n + 1 < p.N && m0 + c + j < m_end)
-                        store_act(p.act_out, p.out_dtype, (int64_t)(m0 + c + j) * p.ldo + (n >> 1), act_gated(p.act, mine, other));
+                        store_act(p.act_out, p.out_dtype, (int64_t)(m0 + c + j) * p.ldo + oc0 + (n >> 1), act_gated(p.act, mine, other));
                 }
             }
         }
@@ -250,8 +254,9 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64
 
 int launch(const void* x, int64_t ldx, const void* w, TcParams p, cudaStream_t st) {
     CUtensorMap mw, mx;
-    const int64_t wrows = p.offs ? (int64_t)p.E * p.N : p.N;
-    if (!make_map(&mw, w, wrows, p.K, p.K) || !make_map(&mx, x, p.M, p.K, ldx)) return fail(B200SEQ_ERR_CUDA, "linear: tensor map encoding failed");
+    const int64_t wrows = p.offs ? (int64_t)p.E * p.N : (p.heads ? (int64_t)p.heads * p.N : p.N);
+    if (!make_map(&mw, w, wrows, p.K, p.K) || !make_map(&mx, x, p.M, p.heads ? (int64_t)p.heads * p.K : p.K, ldx))
+        return fail(B200SEQ_ERR_CUDA, "linear: tensor map encoding failed");
     static bool attr_set = false;
     const int smem = STAGES * STAGE_BYTES + 1024;
     if (!attr_set) {
@@ -260,7 +265,7 @@ int launch(const void* x, int64_t ldx, const void* w, TcParams p, cudaStream_t s
         attr_set = true;
     }
     p.err = error_flag_dev();
-    dim3 grid((p.M + BM - 1) / BM + (p.offs ? p.E : 0), (p.N + BN - 1) / BN);
+    dim3 grid((p.M + BM - 1) / BM + (p.offs ? p.E : 0), (p.N + BN - 1) / BN, p.heads ? p.heads : 1);
     linear_tc_kernel<<<grid, 128, smem, st>>>(mw, mx, p);
     SEQ_LAUNCH_CHECK("linear tc");
     return 0;
@@ -287,6 +292,25 @@ int launch_linear_tc_grouped(const void* x, int64_t ldx, const void* w, const in
     p.M = rows, p.N = N, p.K = K, p.offs = offs, p.E = E;
     if (act_kind < 0) p.y = reinterpret_cast<float*>(out), p.ldy = ldo, p.epi = EPI_NONE;
     else p.act_out = out, p.ldo = ldo, p.out_dtype = out_dtype, p.epi = EPI_PLAIN_ACT, p.act = ActParams{act_kind, 0.f, 0.f, 0.f};
+    return launch(x, ldx, w, p, st);
+}
+
+// per-head form: out[t][h * ocol + n] = sum_k x[t][h * K + k] * w[h][n][k]; act_kind < 0: f32 product, else a plain kind written in out_dtype
+int launch_linear_tc_heads(const void* x, int64_t ldx, const void* w, int T, int H, int N, int K, int act_kind, void* out, int out_dtype, int64_t ldo, int64_t ocol,
+                           cudaStream_t st) {
+    TcParams p{};
+    p.M = T, p.N = N, p.K = K, p.heads = H, p.ocol = ocol;
+    if (act_kind < 0) p.y = reinterpret_cast<float*>(out), p.ldy = ldo, p.epi = EPI_NONE;
+    else p.act_out = out, p.ldo = ldo, p.out_dtype = out_dtype, p.epi = EPI_PLAIN_ACT, p.act = ActParams{act_kind, 0.f, 0.f, 0.f};
+    return launch(x, ldx, w, p, st);
+}
+
+// grouped form with any activation kind (gated kinds: the group's weight rows alternate gate / up, out has N / 2 columns)
+int launch_linear_tc_grouped_act(const void* x, int64_t ldx, const void* w, const int32_t* offs, int E, int rows, int N, int K, const ActParams act, void* out,
+                                 int out_dtype, int64_t ldo, cudaStream_t st) {
+    TcParams p{};
+    p.M = rows, p.N = N, p.K = K, p.offs = offs, p.E = E;
+    p.act_out = out, p.ldo = ldo, p.out_dtype = out_dtype, p.epi = act_kind_gated(act.kind) ? EPI_GATED : EPI_PLAIN_ACT, p.act = act;
     return launch(x, ldx, w, p, st);
 }
 

@@ -16,6 +16,10 @@ constexpr int MOE_MAX_E = 1024;
 bool linear_tc_usable(int x_dtype, int64_t ldx, int M, int N, int K, const void* x, const void* w);
 int launch_linear_tc_grouped(const void* x, int64_t ldx, const void* w, const int32_t* offs, int E, int rows, int N, int K, int act_kind, void* out, int out_dtype,
                              int64_t ldo, cudaStream_t st);
+int launch_linear_tc_heads(const void* x, int64_t ldx, const void* w, int T, int H, int N, int K, int act_kind, void* out, int out_dtype, int64_t ldo, int64_t ocol,
+                           cudaStream_t st);
+int launch_linear_tc_grouped_act(const void* x, int64_t ldx, const void* w, const int32_t* offs, int E, int rows, int N, int K, const ActParams act, void* out,
+                                 int out_dtype, int64_t ldo, cudaStream_t st);
 
 // grid (pairs): row r of the result = the activation row of the token behind the r-th sorted pair (contiguous rows for the tensor-core tiles)
 __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const int32_t* __restrict__ sorted, int x_div, int K,
@@ -223,6 +227,29 @@ __device__ __forceinline__ float ldx<float>(const float* p) { return __ldg(p); }
 template <>
 __device__ __forceinline__ float ldx<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 
+template <typename XT, bool VEC>
+__device__ __forceinline__ float moe_row_dot(const __nv_bfloat16* __restrict__ wr, const XT* __restrict__ xr, int K, int lane) {
+    float acc = 0.f;
+    if (VEC) {
+#pragma unroll 4
+        for (int k = lane * 8; k < K; k += 256) {
+            float wv[8], xv[8];
+            bf16x8_f32(__ldg(reinterpret_cast<const uint4*>(wr + k)), wv);
+            if (sizeof(XT) == 4) {
+                const float4 q0 = __ldg(reinterpret_cast<const float4*>(xr + k)), q1 = __ldg(reinterpret_cast<const float4*>(xr + k) + 1);
+                xv[0] = q0.x, xv[1] = q0.y, xv[2] = q0.z, xv[3] = q0.w, xv[4] = q1.x, xv[5] = q1.y, xv[6] = q1.z, xv[7] = q1.w;
+            } else {
+                bf16x8_f32(__ldg(reinterpret_cast<const uint4*>(xr + k)), xv);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc = fmaf(wv[i], xv[i], acc);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(__bfloat162float(wr[k]), ldx<XT>(xr + k), acc);
+    }
+    return acc;
+}
+
 struct MoeLin {
     const void* x;
     int64_t ldx;
@@ -233,7 +260,26 @@ struct MoeLin {
     void* out;
     int out_dtype;
     int64_t ldo;
+    ActParams gate;   // gated kinds (act = the kind): weight rows alternate (gate j, up j), the result has N / 2 columns
 };
+
+template <typename XT, bool VEC>
+__device__ __forceinline__ float moe_row_dot(const __nv_bfloat16* __restrict__ wr, const XT* __restrict__ xr, int K, int lane);
+
+// gated form of the per-pair rows: grid (blocks of 8 warps over N / 2, pairs): a warp = one (gate, up) pair of rows = one output of one pair
+template <typename XT, bool VEC>
+__global__ void __launch_bounds__(256) moe_rows_gated_kernel(const MoeLin a) {
+    const int lane = threadIdx.x & 31;
+    const int f = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int p = blockIdx.y;
+    if (2 * f + 1 >= a.N) return;
+    const int e = a.ids[p];
+    const __nv_bfloat16* wr = a.w + ((int64_t)e * a.N + 2 * f) * a.K;
+    const XT* xr = reinterpret_cast<const XT*>(a.x) + (int64_t)(a.x_div > 0 ? p / a.x_div : p) * a.ldx;
+    const float g = warp_sum(moe_row_dot<XT, VEC>(wr, xr, a.K, lane));
+    const float u = warp_sum(moe_row_dot<XT, VEC>(wr + a.K, xr, a.K, lane));
+    if (lane == 0) store_act(a.out, a.out_dtype, (int64_t)p * a.ldo + f, act_gated(a.gate, g, u));
+}
 
 // grid (blocks of 8 warps over N, pairs): a warp = one output of one pair
 template <typename XT, bool VEC>
@@ -330,6 +376,19 @@ __global__ void __launch_bounds__(256) moe_tiled_kernel(const MoeLin a) {
         }
         __syncthreads();
     }
+    if (a.act >= 0 && act_is_gated(a.act)) {   // a thread's four columns are two (gate, up) pairs
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = r0 + ty * 4 + i;
+            if (r >= rend) continue;
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int n = n0 + tx * 4 + j;
+                if (n + 1 < a.N) store_act(a.out, a.out_dtype, (int64_t)r * a.ldo + (n >> 1), act_gated(a.gate, acc[i][j], acc[i][j + 1]));
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int r = r0 + ty * 4 + i;
@@ -340,6 +399,78 @@ __global__ void __launch_bounds__(256) moe_tiled_kernel(const MoeLin a) {
             if (n >= a.N) continue;
             if (a.act < 0) reinterpret_cast<float*>(a.out)[(int64_t)r * a.ldo + n] = acc[i][j];
             else store_act(a.out, a.out_dtype, (int64_t)r * a.ldo + n, act_plain(a.act, acc[i][j]));
+        }
+    }
+}
+
+// ---- per-head projections: out[t][h * ocol + n] = sum_k x[t][h * K + k] * w[h][n][k] ---------------------------------------------------------
+struct HeadLin {
+    const void* x;
+    int64_t ldx;
+    const __nv_bfloat16* w;
+    int T, H, N, K, act;
+    void* out;
+    int out_dtype;
+    int64_t ldo, ocol;
+};
+__device__ __forceinline__ void head_store(const HeadLin& a, int64_t idx, float v) {
+    if (a.act < 0) reinterpret_cast<float*>(a.out)[idx] = v;
+    else store_act(a.out, a.out_dtype, idx, act_plain(a.act, v));
+}
+// few (token, head) pairs: grid (blocks of 8 warps over N, T * H), a warp = one output of one pair, the head's weight rows streamed
+template <typename XT, bool VEC>
+__global__ void __launch_bounds__(256) head_rows_kernel(const HeadLin a) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (n >= a.N) return;
+    const int t = blockIdx.y / a.H, h = blockIdx.y - t * a.H;
+    const float acc = warp_sum(moe_row_dot<XT, VEC>(a.w + ((int64_t)h * a.N + n) * a.K, reinterpret_cast<const XT*>(a.x) + (int64_t)t * a.ldx + (int64_t)h * a.K, a.K, lane));
+    if (lane == 0) head_store(a, (int64_t)t * a.ldo + (int64_t)h * a.ocol + n, acc);
+}
+// 64 x 64 f32 fma tiles: grid (N tiles, token tiles, H)
+template <typename XT>
+__global__ void __launch_bounds__(256) head_tiled_kernel(const HeadLin a) {
+    __shared__ float xs[MTK][MT + 4];
+    __shared__ float ws[MTK][MT + 4];
+    const int n0 = blockIdx.x * MT, t0 = blockIdx.y * MT, h = blockIdx.z;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const XT* x = reinterpret_cast<const XT*>(a.x) + (int64_t)h * a.K;
+    const __nv_bfloat16* w = a.w + (int64_t)h * a.N * a.K;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < a.K; k0 += MTK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = threadIdx.x + i * 256;
+            const int r = idx >> 4, kk = idx & 15;
+            const int k = k0 + kk;
+            xs[kk][r] = (t0 + r < a.T && k < a.K) ? ldx<XT>(x + (int64_t)(t0 + r) * a.ldx + k) : 0.f;
+            ws[kk][r] = (n0 + r < a.N && k < a.K) ? __bfloat162float(w[(int64_t)(n0 + r) * a.K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MTK; ++kk) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = xs[kk][ty * 4 + i], bv[i] = ws[kk][tx * 4 + i];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = t0 + ty * 4 + i;
+        if (t >= a.T) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < a.N) head_store(a, (int64_t)t * a.ldo + (int64_t)h * a.ocol + n, acc[i][j]);
         }
     }
 }
@@ -431,14 +562,38 @@ int b200seq_moe_sort(const int32_t* ids, int pairs, int E, const int32_t* counts
 
 int b200seq_moe_linear(const void* x, int x_dtype, int64_t ldx_, int x_div, const void* w, const int32_t* ids, const int32_t* sorted, const int32_t* offs, int pairs,
                        int E, int N, int K, int act, void* out, int out_dtype, int64_t ldo, void* stream) {
-    if (!x || !w || !out || pairs < 0 || E < 1 || N < 1 || K < 1 || ldx_ < K || ldo < N || x_div < 0) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: bad arguments");
+    if (act >= 0 && act_kind_gated(act)) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: only plain activation kinds (gated kinds: b200seq_moe_linear_act)");
+    return b200seq_moe_linear_act(x, x_dtype, ldx_, x_div, w, ids, sorted, offs, pairs, E, N, K, act, 0.f, 0.f, 0.f, out, out_dtype, ldo, stream);
+}
+
+int b200seq_moe_linear_act(const void* x, int x_dtype, int64_t ldx_, int x_div, const void* w, const int32_t* ids, const int32_t* sorted, const int32_t* offs, int pairs,
+                           int E, int N, int K, int act, float limit, float alpha, float shift, void* out, int out_dtype, int64_t ldo, void* stream) {
+    const bool gated = act >= 0 && act_kind_gated(act);
+    if (!x || !w || !out || pairs < 0 || E < 1 || N < 1 || K < 1 || ldx_ < K || ldo < (gated ? N / 2 : N) || x_div < 0 || (gated && (N & 1)))
+        return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: bad arguments");
     if (x_dtype != B200SEQ_F32 && x_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: activation dtype");
-    if (act >= 0 && (!act_kind_known(act) || act_kind_gated(act))) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: only plain activation kinds");
+    if (act >= 0 && !act_kind_known(act)) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: unknown activation kind");
     if (act >= 0 && out_dtype != B200SEQ_F32 && out_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: output dtype");
     if ((sorted == nullptr) != (offs == nullptr) || (!sorted && !ids)) return fail(B200SEQ_ERR_INVALID_ARG, "moe_linear: ids, or sorted with offs");
     if (pairs == 0) return 0;
-    const MoeLin a{x, ldx_, x_div, (const __nv_bfloat16*)w, ids, sorted, offs, pairs, E, N, K, act, out, out_dtype, ldo};
+    const ActParams ap{act, limit, alpha, shift};
+    const MoeLin a{x, ldx_, x_div, (const __nv_bfloat16*)w, ids, sorted, offs, pairs, E, N, K, act, out, out_dtype, ldo, ap};
     cudaStream_t cs = (cudaStream_t)stream;
+    if (!sorted && gated) {
+        const size_t es = x_dtype == B200SEQ_F32 ? 4 : 2;
+        const bool vec = K % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (ldx_ * es) % 16 == 0;
+        if (pairs > 65535) return fail(B200SEQ_ERR_UNSUPPORTED, "moe_linear: too many pairs for the row form");
+        dim3 grid((N / 2 + 7) / 8, pairs);
+        if (x_dtype == B200SEQ_F32) {
+            if (vec) moe_rows_gated_kernel<float, true><<<grid, 256, 0, cs>>>(a);
+            else moe_rows_gated_kernel<float, false><<<grid, 256, 0, cs>>>(a);
+        } else {
+            if (vec) moe_rows_gated_kernel<__nv_bfloat16, true><<<grid, 256, 0, cs>>>(a);
+            else moe_rows_gated_kernel<__nv_bfloat16, false><<<grid, 256, 0, cs>>>(a);
+        }
+        SEQ_LAUNCH_CHECK("moe_linear gated rows");
+        return 0;
+    }
     if (!sorted) {
         const size_t es = x_dtype == B200SEQ_F32 ? 4 : 2;
         const bool vec = K % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (ldx_ * es) % 16 == 0;
@@ -454,14 +609,49 @@ int b200seq_moe_linear(const void* x, int x_dtype, int64_t ldx_, int x_div, cons
         SEQ_LAUNCH_CHECK("moe_linear rows");
         return 0;
     }
-    if (x_div == 0 && pairs >= 32 && linear_tc_usable(x_dtype, ldx_, pairs, N, K, x, w))   // rows laid out like the result: tcgen05 tiles per expert
+    if (x_div == 0 && pairs >= 32 && linear_tc_usable(x_dtype, ldx_, pairs, N, K, x, w)) {   // rows laid out like the result: tcgen05 tiles per expert
+        if (gated) return launch_linear_tc_grouped_act(x, ldx_, w, offs, E, pairs, N, K, ap, out, out_dtype, ldo, cs);
         return launch_linear_tc_grouped(x, ldx_, w, offs, E, pairs, N, K, act, out, out_dtype, ldo, cs);
+    }
     const int tiles = (pairs + MT - 1) / MT + E;
     if (tiles > 65535) return fail(B200SEQ_ERR_UNSUPPORTED, "moe_linear: too many row tiles");
     dim3 grid((N + MT - 1) / MT, tiles);
     if (x_dtype == B200SEQ_F32) moe_tiled_kernel<float><<<grid, 256, 0, cs>>>(a);
     else moe_tiled_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(a);
     SEQ_LAUNCH_CHECK("moe_linear tiles");
+    return 0;
+}
+
+int b200seq_head_linear(const void* x, int x_dtype, int64_t ldx_, const void* w, int T, int H, int N, int K, int act, void* out, int out_dtype, int64_t ldo, int64_t ocol,
+                        void* stream) {
+    if (!x || !w || !out || T < 0 || H < 1 || N < 1 || K < 1 || ldx_ < (int64_t)H * K || ocol < N || ldo < (int64_t)(H - 1) * ocol + N)
+        return fail(B200SEQ_ERR_INVALID_ARG, "head_linear: bad arguments");
+    if (x_dtype != B200SEQ_F32 && x_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "head_linear: activation dtype");
+    if (act >= 0 && (!act_kind_known(act) || act_kind_gated(act) || (out_dtype != B200SEQ_F32 && out_dtype != B200SEQ_BF16)))
+        return fail(B200SEQ_ERR_INVALID_ARG, "head_linear: a plain activation kind and an output dtype");
+    if (T == 0) return 0;
+    if (H > 65535 || (int64_t)T * H > 65535 * 64) return fail(B200SEQ_ERR_UNSUPPORTED, "head_linear: too many heads or tokens in one step");
+    const HeadLin a{x, ldx_, (const __nv_bfloat16*)w, T, H, N, K, act, out, out_dtype, ldo, ocol};
+    cudaStream_t cs = (cudaStream_t)stream;
+    const size_t es = x_dtype == B200SEQ_F32 ? 4 : 2;
+    if ((int64_t)T * H <= 64) {
+        const bool vec = K % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (ldx_ * es) % 16 == 0;
+        dim3 grid((N + 7) / 8, T * H);
+        if (x_dtype == B200SEQ_F32) {
+            if (vec) head_rows_kernel<float, true><<<grid, 256, 0, cs>>>(a);
+            else head_rows_kernel<float, false><<<grid, 256, 0, cs>>>(a);
+        } else {
+            if (vec) head_rows_kernel<__nv_bfloat16, true><<<grid, 256, 0, cs>>>(a);
+            else head_rows_kernel<__nv_bfloat16, false><<<grid, 256, 0, cs>>>(a);
+        }
+        SEQ_LAUNCH_CHECK("head_linear rows");
+        return 0;
+    }
+    if (T >= 32 && linear_tc_usable(x_dtype, ldx_, T, N, K, x, w)) return launch_linear_tc_heads(x, ldx_, w, T, H, N, K, act, out, out_dtype, ldo, ocol, cs);
+    dim3 grid((N + MT - 1) / MT, (T + MT - 1) / MT, H);
+    if (x_dtype == B200SEQ_F32) head_tiled_kernel<float><<<grid, 256, 0, cs>>>(a);
+    else head_tiled_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(a);
+    SEQ_LAUNCH_CHECK("head_linear tiles");
     return 0;
 }
 

@@ -206,7 +206,6 @@ class _Workspace:
             self.oup = torch.empty((cap, max(1, model.max_inner)), **act)
             self.ff_inner = torch.empty((cap, max(1, model.max_ff_inner)), **act)
             self.ff_proj = torch.empty((cap, max(1, model.max_ff_proj)), **f32)
-            self.head_ids = {H: (torch.arange(cap * H, dtype=torch.int32) % H).to(dev) for H in model.latent_heads}
         mo = model.moe_dims
         if mo is not None:              # mixture of experts: router logits, choices, sort, per-pair intermediates
             E1, top, F = mo
@@ -219,7 +218,6 @@ class _Workspace:
             self.moe_order = torch.empty((cap * top,), **i32)
             self.moe_slot = torch.empty((cap * top,), **i32)
             self.moe_act = torch.empty((cap * top, F), **act)
-            self.moe_z2 = torch.empty((cap * top, 2 * F), **f32) if model.moe_gated else None      # gate | up products of gated experts
             self.moe_ys = torch.empty((cap * top, W), **f32)
             self.moe_sh = torch.empty((cap, W), **f32)
             self.moe_xs = torch.empty((cap * top, W), **act) if model.act_dtype == torch.bfloat16 else None   # tokens' rows in sorted pair order
@@ -289,9 +287,8 @@ class LayeredModel:
         self.max_proj = self.max_xbc = self.max_inner = 1
         self.max_ff_inner = self.max_ff_proj = 1      # depth layout: sizes of the feed-forward branch's own intermediates
         self.moe_dims = None      # (experts + 1, top, expert ff): largest over the layers
-        self.moe_gated = False    # some layer's experts have a gate branch
         self.max_q = self.max_qp = self.max_qn = 1      # latent attention: query rows, latent-space query rows, unrotated query parts
-        self.latent_heads = set()
+        self.max_ctx_r = self.max_ctx_kv = 0            # latent attention: latent size, per-head keys | values of one position
         self.weight_bytes = self.embed.numel() * 2 + (0 if cfg.tied_head else self.head.numel() * 2)
         for i, ls in enumerate(cfg.layers):
             if post:
@@ -396,6 +393,8 @@ class LayeredModel:
         self.use_graphs = True
         self.overlap_branches = True     # depth layout: mixer and feed-forward of a layer on two streams
         self._side = self._side2 = None
+        self._ctx_rows = 0       # steps with prompt portions: positions in the contexts of all entries (latent attention projects keys / values out of them)
+        self._ctx_cap, self._ctx = 0, None
 
     # ---- layout "post": weights of one layer -------------------------------------------------------------------------------------------
     def _post_layer(self, i: int, ls: "LayerSpec", lin, vec, get) -> Dict[str, object]:
@@ -462,6 +461,7 @@ class LayeredModel:
                 raise ValueError(f"layer {i}: latent-attention tensor shapes do not fit the configuration")
             L["w_ukT"] = uk.view(H, Dn, R).transpose(1, 2).contiguous()      # [H][R][Dn]: the query's way into the latent space
             L["w_uv"] = uv.view(H, V, R).contiguous()
+            L["w_ukv"] = torch.cat([uk, uv], 0).contiguous()                 # steps of prompt portions: per-head keys | values out of the gathered latents
             L["sink"] = vec(p + "mix.sink") if m.sink else None
             if m.sink and L["sink"].numel() != H:
                 raise ValueError(f"layer {i}: one sink per head expected")
@@ -497,7 +497,6 @@ class LayeredModel:
                 raise ValueError(f"layer {i}: unknown router kind {f.router}")
             if gated:
                 L["w_eup"] = torch.stack([gate_up(p + f"mlp.e{e}.", f.ff) for e in range(f.experts)]).contiguous()
-                self.moe_gated = True
             else:
                 L["w_eup"] = torch.stack([lin(p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
             L["w_edown"] = torch.stack([lin(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
@@ -532,7 +531,7 @@ class LayeredModel:
             self.max_q = max(self.max_q, m.heads * (m.dim + m.rot_dim), m.vdim)
             self.max_qp = max(self.max_qp, m.heads * (m.kv_rank + m.rot_dim))
             self.max_qn = max(self.max_qn, m.heads * m.dim)
-            self.latent_heads.add(m.heads)
+            self.max_ctx_r, self.max_ctx_kv = max(self.max_ctx_r, m.kv_rank), max(self.max_ctx_kv, m.heads * (m.dim + m.vdim))
         if isinstance(f, MoeFfSpec):
             md = self.moe_dims or (1, 1, 1)
             self.moe_dims = (max(md[0], f.experts + 1), max(md[1], f.top), max(md[2], f.ff))
@@ -564,6 +563,8 @@ class LayeredModel:
                 L["ret_state"] = torch.zeros((max_seqs, m.heads, m.dim, m.vdim), **f32)
             elif ls.kind == "latent_attention":       # one row [latent | rotated key part] per position; keys and values of all heads come out of it
                 L["kpool"] = torch.zeros((max(1, num_blocks), block_size, m.kv_rank + m.rot_dim), **f32)
+                L["desc_x"] = seqops.expanded_attn_desc(m.heads, m.dim, m.rot_dim, m.vdim, m.scale, L["kpool"].view(-1, m.kv_rank + m.rot_dim)[:, m.kv_rank:],
+                                                        gated=m.gated, sink=L["sink"])
             elif ls.kind == "attention":
                 L["kpool"] = torch.zeros((max(1, num_blocks), block_size, m.kv_heads, m.dim), **f32)
                 L["vpool"] = torch.zeros((max(1, num_blocks), block_size, m.kv_heads, m.vdim), **f32)
@@ -592,7 +593,8 @@ class LayeredModel:
                 if key not in seen:
                     seen.add(key)
                     ctx = self.max_blocks * self.block_size
-                    need = max([need] + [seqops.attn_scratch_floats(T, 1, m.heads, 1, m.kv_rank, ctx) for T in range(1, cap + 1)])
+                    need = max([need] + [max(seqops.attn_scratch_floats(T, 1, m.heads, 1, m.kv_rank, ctx), seqops.attn_scratch_floats(T, 1, m.heads, m.heads, m.vdim, ctx))
+                                         for T in range(1, cap + 1)])
             else:
                 ctx = keys = self.max_blocks * self.block_size
                 keys = min(keys, m.chunk) if m.chunk > 0 else keys
@@ -607,6 +609,17 @@ class LayeredModel:
     def cache_bytes(self) -> int:
         keys = ("canon1_state", "canon2_state", "kpool", "vpool", "kpooled", "vpooled", "conv_state", "ssm_state", "shift_state", "ret_state")
         return sum(L[k].numel() * 4 for L in self.layers for k in keys if k in L)
+
+    def _ctx_buffers(self, rows: int):
+        """gathered latents (activation type) and the per-head keys | values projected out of them (f32) for `rows` context positions;
+        grown on demand, shared by all latent-attention layers"""
+        cap = 256
+        while cap < rows:
+            cap *= 2
+        if self._ctx_cap < cap:
+            self._ctx = (torch.empty((cap, self.max_ctx_r), dtype=self.act_dtype, device=self.dev), torch.empty((cap, self.max_ctx_kv), dtype=torch.float32, device=self.dev))
+            self._ctx_cap = cap
+        return self._ctx
 
     def _workspace(self, T: int) -> _Workspace:
         cap = 8
@@ -648,6 +661,7 @@ class LayeredModel:
         if not self.block_size:
             raise RuntimeError("allocate() the cache first")
         T, B, R = sa.T, sa.B, int(sa.want_rows.shape[0])
+        self._ctx_rows = int(sa.ent_pos0.sum()) + T if (T > B and self.max_ctx_r) else 0
         ws = self._workspace(T)
         self._upload(ws, sa)
         graphable = self.use_graphs and debug_layers is None and sa.decode_only and R == T and self.dev.type == "cuda" \
@@ -807,6 +821,9 @@ class LayeredModel:
         seqops.linear(o, L["w_o"], y)
 
     def _latent_attention(self, L, m: LatentAttentionSpec, ws: _Workspace, st, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
+        """Two forms with the same result.  Single-token steps stay in the latent space (the cache is read as it is: H query heads of size
+        kv_rank + rot_dim over one key head).  Steps with prompt portions gather the latents of the entries' contexts, project per-head keys and
+        values out of them once, and attend with heads of size dim + rot_dim: far fewer operations per (query, key) pair."""
         H, Dn, Rd, V, R, Rq = m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank
         eps = self.cfg.eps
         proj = ws.proj[:T, :L["w_in"].shape[0]]
@@ -815,38 +832,29 @@ class LayeredModel:
         seqops.group_rmsnorm(proj[:, :Rq], L["dq_norm"], 1, eps, cq)
         q = ws.q.view(-1)[:T * H * (Dn + Rd)].view(T, H * (Dn + Rd))
         seqops.linear(cq, L["w_uq"], q)
+        gate = proj[:, Rq + R + Rd:] if m.gated else None
+        if self._ctx_rows > 0:
+            ctx = self._ctx_rows
+            seqops.latent_prep(proj, Rq, -1, q, st, H, Dn, Rd, R, L["kv_norm"], eps, L["rot_freq"], L["rot_scale"], L["kpool"], None, None)
+            cx, kvx = self._ctx_buffers(ctx)
+            cx = cx.view(-1)[:ctx * R].view(ctx, R)
+            kvx = kvx.view(-1)[:ctx * H * (Dn + V)].view(ctx, H * (Dn + V))
+            seqops.latent_gather(L["kpool"], st, R, ctx, cx)
+            seqops.linear(cx, L["w_ukv"], kvx)
+            up = ws.oup.view(-1)[:T * H * V].view(T, H * V)
+            seqops.attn_ex(q, st, L["desc_x"], kvx, kvx[:, H * Dn:], up, ws.scratch, gate=gate)
+            seqops.linear(up, L["w_o"], y)
+            return
         Qp = ws.Qp.view(-1)[:T * H * (R + Rd)].view(T, H * (R + Rd))
-        qn = ws.qn.view(-1)[:T * H * Dn].view(T * H, Dn)
+        qn = ws.qn.view(-1)[:T * H * Dn].view(T, H * Dn)
         seqops.latent_prep(proj, Rq, -1, q, st, H, Dn, Rd, R, L["kv_norm"], eps, L["rot_freq"], L["rot_scale"], L["kpool"], Qp, qn)
         # the unrotated query parts enter the latent space head by head: Qp[t][h][:R] = W_uk[h]^T q_nope[t][h]
-        self._head_linear(ws, T, H, qn, L["w_ukT"], Qp.view(T * H, R + Rd)[:, :R], None)
+        seqops.head_linear(qn, L["w_ukT"], Qp, R + Rd)
         o = ws.inner_a.view(-1)[:T * H * R].view(T, H * R)
-        gate = proj[:, Rq + R + Rd:] if m.gated else None
         seqops.attn_ex(Qp, st, L["desc"], L["kpool"], None, o, ws.scratch, gate=gate)
         up = ws.oup.view(-1)[:T * H * V].view(T, H * V)
-        self._head_linear(ws, T, H, o.view(T * H, R), L["w_uv"], up.view(T * H, V), ws.q)      # values leave the latent space after the weighted sum
+        seqops.head_linear(o, L["w_uv"], up, V, seqops.ACT_IDENT)      # values leave the latent space after the weighted sum
         seqops.linear(up, L["w_o"], y)
-
-    HEAD_ROW_PAIRS = 64     # up to this many (token, head) pairs one launch streams every head's weight per pair; more: one product per head
-
-    def _head_linear(self, ws: _Workspace, T: int, H: int, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tmp: Optional[torch.Tensor]) -> None:
-        """out[t * H + h] = w[h] . x[t * H + h] for every (token, head): x [T * H, K] rows, w bf16 [H, N, K], out [T * H, N] rows (f32: the product;
-        activation type: the product written in that type, `tmp` holds the f32 product where no fused path takes the step)"""
-        ops = seqops
-        pairs = T * H
-        to_act = out.dtype != torch.float32 or tmp is not None
-        if pairs <= self.HEAD_ROW_PAIRS:
-            ops.moe_linear(x, 0, w, ws.head_ids[H], None, None, pairs, ops.ACT_IDENT if to_act else ops.ACT_NONE, out)
-            return
-        K, N = x.shape[1], out.shape[1]
-        xs, os_ = x.stride(0), out.stride(0)
-        for h in range(H):
-            xh = x.as_strided((T, K), (H * xs, 1), x.storage_offset() + h * xs)
-            oh = out.as_strided((T, N), (H * os_, 1), out.storage_offset() + h * os_)
-            if to_act:
-                self._proj_act(tmp, T, xh, w[h], ops.ACT_IDENT, oh)
-            else:
-                ops.linear(xh, w[h], oh)
 
     def _run_streams(self, ws: _Workspace, T: int, B: int, R: int, sample: bool, debug_layers: Optional[list]) -> None:
         cfg = self.cfg
@@ -938,9 +946,7 @@ class LayeredModel:
                 ops.moe_route(z, E, f.groups, f.keep, top, ws.moe_ids, ws.moe_wts, None if rows_form else ws.moe_cnt)
         kind = ops.ACT_KINDS[f.act]
         mid = ws.moe_act.view(-1)[:pairs * f.ff].view(pairs, f.ff)
-        up_out, up_kind = mid, kind
-        if kind in ops.ACT_GATED:       # gated experts: the gate | up product of every pair (rows alternate), then the activation
-            up_out, up_kind = ws.moe_z2.view(-1)[:pairs * 2 * f.ff].view(pairs, 2 * f.ff), ops.ACT_NONE
+        act_args = (f.limit, f.alpha, f.up_shift) if kind in ops.ACT_GATED else ()     # gated experts: activation of the (gate, up) pairs in the projection's epilogue
         ys = ws.moe_ys[:pairs]
         if rows_form:
             order = offs = slot = None
@@ -950,11 +956,9 @@ class LayeredModel:
         if not rows_form and ws.moe_xs is not None and ops.tc_usable(a, a.shape[1]) and f.ff % 8 == 0:
             xs = ws.moe_xs[:pairs]                  # tensor-core tiles fetch contiguous rows: put the tokens' rows in sorted order first
             ops.moe_gather(a, top, order, pairs, xs)
-            ops.moe_linear(xs, 0, L["w_eup"], ws.moe_ids, order, offs, pairs, up_kind, up_out)
+            ops.moe_linear(xs, 0, L["w_eup"], ws.moe_ids, order, offs, pairs, kind, mid, *act_args)
         else:
-            ops.moe_linear(a, top, L["w_eup"], ws.moe_ids, order, offs, pairs, up_kind, up_out)
-        if up_out is not mid:
-            ops.act(up_out, kind, mid, f.limit, f.alpha, f.up_shift)
+            ops.moe_linear(a, top, L["w_eup"], ws.moe_ids, order, offs, pairs, kind, mid, *act_args)
         ops.moe_linear(mid, 0, L["w_edown"], ws.moe_ids, order, offs, pairs, ops.ACT_NONE, ys)
         sh = None
         if shared_done is not None:

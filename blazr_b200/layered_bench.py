@@ -6,9 +6,10 @@ dense-attention decoder (blazr_b200/decode.py, Q8_0 weights) of the same width, 
     kernels  : every operator of one prefill step and one decode step timed alone (CUDA events around each launch), with its
                algorithmic bytes / FLOPs and the fraction of the roofline it reaches; the like kernels of the decoder beside them
 
-`python bench.py --layered fenorax|gemosun [--layered-sizes w1024,w2048]` prints the result as one JSON line; bench.py's default
+`python bench.py --layered fenorax|gemosun|teselix [--layered-sizes w1024,w2048]` prints the result as one JSON line; bench.py's default
 workload and JSON line are untouched.  For Gemosun (parallel attention / feed-forward layers, three of four feed-forwards a mixture of
-experts) the closest existing model, Fenorax at the same sizes, runs beside it as well.
+experts) the closest existing model, Fenorax at the same sizes, runs beside it as well; for Teselix (retention and latent-attention mixers,
+table-routed experts) both run beside it: Gemosun is the closest in attention and experts, Fenorax in the recurrence.
 """
 from __future__ import annotations
 
@@ -53,6 +54,60 @@ def gemosun_config(sz: dict, experts: int = 32, top: int = 4) -> dict:
     moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": eff}}
     return {"architecture": "Gemosun", "vocab": sz["vocab"], "width": sz["width"], "norm": {"eps": 1e-5},
             "layers": [att({"kind": "dense", "ff": sz["ff"]}), att(dict(moe)), att(dict(moe)), att(dict(moe))]}
+
+
+def teselix_config(sz: dict, experts: int = 32, top: int = 4, kv_rank: int = 256) -> dict:
+    """four post-norm layers [retention, latent attention] x 2 of the size's width and head layout, every one with table-routed experts (an
+    expert a quarter of the dense size, `top` per token) and a shared expert; retention heads of the size's head size with decays spread
+    between 1 - 2^-5 and 1 - 2^-12; latent attention with a key / value latent of `kv_rank`, a query latent of 3/8 of the width and a rotated
+    part of half a head"""
+    H, D, W = sz["heads"], sz["dim"], sz["width"]
+    eff = sz["ff"] // 4
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": experts, "top": top}, "shared": {"ff": eff, "limit": 7.0}}
+    ret = {"type": "retention", "mlp": dict(moe),
+           "mixer": {"heads": H, "dim": D, "vdim": D, "decay": [1.0 - 2.0 ** (-5.0 - 7.0 * h / max(H - 1, 1)) for h in range(H)], "rot": {"dims": D, "base": 1e6}}}
+    lat = {"type": "latent_attention", "mlp": dict(moe),
+           "mixer": {"heads": H, "dim": D, "rot_dim": D // 2, "vdim": D, "q_rank": 3 * W // 8, "kv_rank": kv_rank, "scale": (D + D // 2) ** -0.5,
+                     "rot": {"dims": D // 2, "base": 10000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    return {"architecture": "Teselix", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "postln_alpha": 2.0, "layers": [ret, lat, dict(ret), dict(lat)]}
+
+
+def random_tensors_teselix(cfg: dict, device, seed: int = 7):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(shape, generator=g, device=device) * scale).to(torch.bfloat16)
+
+    ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device=device)
+    zeros = lambda n: torch.zeros(n, dtype=torch.bfloat16, device=device)
+    t = {"embed": rnd(V, W), "final.norm": ones(W), "final.norm.b": zeros(W)}
+    for i, lay in enumerate(cfg["layers"]):
+        p, m, mlp = f"l{i}.", lay["mixer"], lay["mlp"]
+        H = m["heads"]
+        for q in ("1", "2"):
+            t[p + "norm" + q], t[p + "norm" + q + ".b"] = ones(W), zeros(W)
+            t[p + "rg" + q], t[p + "rg" + q + ".b"] = rnd(W, W, scale=W ** -0.5), zeros(W)
+        t[p + "shift"] = torch.full((W,), 0.5, dtype=torch.bfloat16, device=device)
+        if lay["type"] == "retention":
+            D, Vd = m["dim"], m["vdim"]
+            t[p + "mix.q"], t[p + "mix.k"] = rnd(H * D, W, scale=W ** -0.5), rnd(H * D, W, scale=W ** -0.5)
+            t[p + "mix.v"], t[p + "mix.g"], t[p + "mix.o"] = rnd(H * Vd, W, scale=W ** -0.5), rnd(H * Vd, W, scale=W ** -0.5), rnd(W, H * Vd, scale=(H * Vd) ** -0.5)
+        else:
+            D, Rd, Vd, R, Rq = m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            t[p + "mix.dq"], t[p + "mix.dq.norm"], t[p + "mix.uq"] = rnd(Rq, W, scale=W ** -0.5), ones(Rq), rnd(H * (D + Rd), Rq, scale=Rq ** -0.5)
+            t[p + "mix.dkv"], t[p + "mix.dkv.norm"] = rnd(R + Rd, W, scale=W ** -0.5), ones(R)
+            t[p + "mix.uk"], t[p + "mix.uv"] = rnd(H * D, R, scale=R ** -0.5), rnd(H * Vd, R, scale=R ** -0.5)
+            t[p + "mix.sink"], t[p + "mix.g"], t[p + "mix.o"] = zeros(H), rnd(H, W, scale=W ** -0.5), rnd(W, H * Vd, scale=(H * Vd) ** -0.5)
+        E, top, ff, sf = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"], mlp["shared"]["ff"]
+        for e in range(E):
+            t[p + f"mlp.e{e}.gate"], t[p + f"mlp.e{e}.up"], t[p + f"mlp.e{e}.down"] = rnd(ff, W, scale=W ** -0.5), rnd(ff, W, scale=W ** -0.5), rnd(W, ff, scale=ff ** -0.5)
+        t[p + "mlp.shared.gate"], t[p + "mlp.shared.up"], t[p + "mlp.shared.down"] = rnd(sf, W, scale=W ** -0.5), rnd(sf, W, scale=W ** -0.5), rnd(W, sf, scale=sf ** -0.5)
+        # every row names `top` different experts: a random start and a stride that is coprime to the expert count
+        start = torch.randint(0, E, (V, 1), generator=g, device=device)
+        t[p + "mlp.table"] = ((start + torch.arange(top, device=device)[None, :] * (E // top if E % top == 0 else 1)) % E).to(torch.int32)
+    return t.__getitem__
 
 
 def random_tensors_gemosun(cfg: dict, device, seed: int = 7):
@@ -130,7 +185,7 @@ def _events():
 
 def _linear_weights(model: LayeredModel) -> int:
     """weights of the linear layers a token goes through (of a mixture of experts: the router, the chosen experts, the shared one)"""
-    n = sum(L[k].numel() for L in model.layers for k in ("w_in", "w_o", "w_gu", "w_down", "w_router", "w_sup", "w_sdown") if k in L)
+    n = sum(L[k].numel() for L in model.layers for k in ("w_in", "w_o", "w_gu", "w_down", "w_router", "w_sup", "w_sdown", "rg1", "rg2", "w_uq", "w_ukT", "w_uv") if k in L)
     for L in model.layers:
         if "w_eup" in L:
             n += L["spec"].ff.top * (L["w_eup"][0].numel() + L["w_edown"][0].numel())
@@ -167,6 +222,29 @@ def _cost(name: str, shapes, scal, scen: dict, kw: dict = None):
         rows_in = pairs if scal[0] == 0 else xs[0]
         w_read = min(E, pairs) * N * K * 2           # every expert that has a pair streams its weight once
         return rows_in * K * xe + w_read + pairs * N * oe, 2.0 * pairs * N * K, "tensor"
+    if name == "retention":       # the projection row in, the gated result out, the state of every entry read and written; recurrence + chunk products
+        d = scen["ret_desc"]
+        T, ld = sh[0][0]
+        B = scen["entries"]
+        flops = 2.0 * T * d.H * (3 * d.D * d.V if scen["prefill"] else 2 * d.D * d.V)      # state update, output (chunked: + the local state), without the chunk's own scores
+        if scen["prefill"]:
+            flops += 2.0 * T * d.H * 32 * (d.D + d.V)                                       # on average 32 of the chunk's 64 keys are at or before a token
+        return T * (ld * 4 + d.H * d.V * sh[2][1]) + 2 * B * d.H * d.D * d.V * 4, flops, "f32" if scen["prefill"] else "hbm"
+    if name == "latent_prep":     # projection row and query row in, pool row, rotated query parts and unrotated parts out
+        (T, ldp), (_, ldq) = sh[0][0], sh[1][0]
+        return T * (ldp + 2 * ldq) * 4, 0.0, "hbm"
+    if name == "post_norm":       # x (+ result + gate logits) in, x and the activation rows out
+        rows = kw["rows"][0][0] if isinstance(kw.get("rows"), tuple) else sh[0][0][0]
+        W = sh[0][0][1]
+        reads = 1 + sum(1 for n in ("y", "zg") if isinstance(kw.get(n), tuple))
+        outs = sum(kw[n][1] for n in ("x_out", "a_out", "a_shift_out") if isinstance(kw.get(n), tuple))
+        return rows * W * (4 * reads + outs), 0.0, "hbm"
+    if name == "token_shift":
+        (T, W), outs = sh[0][0], sum(s[1] for s in sh[3:])
+        return T * W * (4 + outs), 0.0, "hbm"
+    if name == "moe_table_route":
+        T, top = scal[0], scal[2]
+        return T * 4 + T * top * 12, 0.0, "hbm"
     if name in ("attn", "attn_ex"):
         if name == "attn_ex":
             d = scen["attn_desc"]
@@ -174,7 +252,7 @@ def _cost(name: str, shapes, scal, scen: dict, kw: dict = None):
         else:
             T, H, G, D, V = sh[0][0][0], scal[0], scal[1], scal[2], scal[3]
         keys = scen["visible_keys"]                              # sum over the step's tokens of the keys each one sees
-        kv_once = scen["kv_rows_touched"] * G * (D + V) * 4      # every visible K / V row once
+        kv_once = scen["kv_rows_touched"] * G * (D if getattr(d, "latent_v", 0) else D + V) * 4 if name == "attn_ex" else scen["kv_rows_touched"] * G * (D + V) * 4   # every visible K / V row once
         return kv_once + T * H * (D + V) * 4, 2.0 * keys * H * (D + V), "f32" if scen["prefill"] else "hbm"
     if name == "ssm_scan":
         T, (H, V, N, G) = sh[0][0][0], scal[2:6]
@@ -241,20 +319,24 @@ def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, ba
     elif design.lower() == "gemosun":
         cfg = gemosun_config(sz)
         model = LayeredModel(registry.LAYERED["Gemosun"](cfg), random_tensors_gemosun(cfg, dev), dev, dtype)
+    elif design.lower() == "teselix":
+        cfg = teselix_config(sz)
+        model = LayeredModel(registry.LAYERED["Teselix"](cfg), random_tensors_teselix(cfg, dev), dev, dtype)
     else:
         raise ValueError(f"no synthetic workload for design '{design}'")
-    gem = design.lower() == "gemosun"
+    gem, tes = design.lower() == "gemosun", design.lower() == "teselix"
     pool = 16 if gem else 0
-    desc0 = next((L["desc"] for L in model.layers if "desc" in L), None)
+    desc0 = next((L["desc"] for L in model.layers if isinstance(L.get("desc"), seqops.AttnDesc)), None)
+    rdesc0 = next((L["desc"] for L in model.layers if isinstance(L.get("desc"), seqops.RetentionDesc)), None)
     Bmax = max(batches)
     eng = Engine(model, max_tokens=max(S, Bmax * (ctx + steps + 64)) + 64, max_seqs=Bmax, max_step_tokens=max(S, 2048), prefill_chunk=S)
     rng = np.random.default_rng(3)
     prompt = rng.integers(0, sz["vocab"], S).tolist()
     out = {"size": size, "config": {k: sz[k] for k in sz}, "layers": [l["type"] + ("+" + l["mlp"].get("kind", "ff") if l["mlp"] else "") for l in cfg["layers"]],
            "streams": cfg.get("streams", 1), "linear_weights": _linear_weights(model), "weight_bytes": model.weight_bytes}
-    if gem:
+    if gem or tes:
         r = cfg["layers"][1]["mlp"]
-        out["experts"] = {"experts": r["router"]["experts"], "top": r["router"]["top"], "ff": r["expert"]["ff"], "shared_ff": r["shared"]["ff"], "groups": r["router"]["groups"]}
+        out["experts"] = {"experts": r["router"]["experts"], "top": r["router"]["top"], "ff": r["expert"]["ff"], "shared_ff": r["shared"]["ff"], "groups": r["router"].get("groups")}
     lin_flops_tok = 2.0 * (_linear_weights(model) + 0)
 
     # prefill: whole prompt in one step, logits of the last token, device timed; then through run_entries (host arrays in, logits out)
@@ -287,6 +369,8 @@ def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, ba
     if gem:     # window of `chunk` positions plus one pooled entry per block of 16 wholly before it
         vis = np.minimum(pos + 1, chunk) + np.maximum(0, (pos - chunk + 1) // pool)
         scen = dict(prefill=True, entries=1, visible_keys=int(vis.sum()), kv_rows_touched=S + S // pool, attn_desc=desc0)
+    elif tes:   # every earlier position
+        scen = dict(prefill=True, entries=1, visible_keys=int((pos + 1).sum()), kv_rows_touched=S, attn_desc=desc0, ret_desc=rdesc0)
     else:
         scen = dict(prefill=True, entries=1, visible_keys=int((pos - (pos // chunk) * chunk + 1).sum()), kv_rows_touched=S, attn_desc=desc0)
     out["prefill"]["kernels"] = kernel_table(model, eng, prefill_once, scen, pk)
@@ -332,8 +416,8 @@ def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, ba
                "frac_hbm_weights_only": round(touched / (msd * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
         held = eng.cache.live[ids[0]].n_tokens
         lo = (held // chunk) * chunk
-        seen = (min(held + 1, chunk) + max(0, (held - chunk + 1) // pool)) if gem else held - lo + 1
-        scen = dict(prefill=False, entries=B, visible_keys=B * seen, kv_rows_touched=B * seen, attn_desc=desc0)
+        seen = (min(held + 1, chunk) + max(0, (held - chunk + 1) // pool)) if gem else (held + 1 if tes else held - lo + 1)
+        scen = dict(prefill=False, entries=B, visible_keys=B * seen, kv_rows_touched=B * seen, attn_desc=desc0, ret_desc=rdesc0)
         row["kernels"] = kernel_table(model, eng, dec_step, scen, pk)
         out["decode"].append(row)
         for r in ids:
@@ -489,11 +573,12 @@ def run(design: str, sizes: List[str], pk, pk_kind: str, S: int = 4096, ctx: int
     for size in sizes:
         row = {"size": size}
         row[design.lower()] = bench_layered(design, size, pk, S=S, ctx=ctx, steps=steps)
-        if design.lower() != "fenorax":     # the closest existing layer-list model at the same sizes
+        others = {"fenorax": [], "gemosun": ["fenorax"], "teselix": ["gemosun", "fenorax"]}.get(design.lower(), ["fenorax"])
+        for other in others:                # the closest existing layer-list models at the same sizes
             try:
-                row["fenorax"] = bench_layered("fenorax", size, pk, S=S, ctx=ctx, steps=steps)
+                row[other] = bench_layered(other, size, pk, S=S, ctx=ctx, steps=steps)
             except Exception as ex:
-                row["fenorax"] = {"error": repr(ex)[:300]}
+                row[other] = {"error": repr(ex)[:300]}
         try:
             row["dense_decoder"] = bench_decoder(size, pk, S=S, ctx=ctx, steps=steps)
         except Exception as ex:    # the comparison arm must not take the design's numbers down

@@ -34,7 +34,7 @@ _DT = {torch.float32: F32, torch.bfloat16: BF16}
 EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b200seq_error_flags", "b200seq_embed_streams", "b200seq_hc_norm", "b200seq_hc_norm_conv",
            "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_linear_gated", "b200seq_attn_prep", "b200seq_attn", "b200seq_attn_scratch_floats",
            "b200seq_ssm_scan", "b200seq_ssm_scratch_floats", "b200seq_argmax", "b200seq_linear_act", "b200seq_act", "b200seq_depth_norm", "b200seq_attn_prep_ex",
-           "b200seq_attn_ex", "b200seq_moe_route", "b200seq_moe_sort", "b200seq_moe_linear", "b200seq_moe_gather", "b200seq_moe_combine", "b200seq_moe_router", "b200seq_moe_table_route",
+           "b200seq_attn_ex", "b200seq_moe_route", "b200seq_moe_sort", "b200seq_moe_linear", "b200seq_moe_gather", "b200seq_moe_combine", "b200seq_moe_router", "b200seq_moe_table_route", "b200seq_moe_linear_act", "b200seq_head_linear", "b200seq_latent_gather",
            "b200seq_latent_prep", "b200seq_rotary", "b200seq_retention", "b200seq_retention_scratch_floats", "b200seq_token_shift", "b200seq_post_norm"]
 
 
@@ -54,7 +54,7 @@ class AttnDesc(C.Structure):
     """b200seq_attn_desc: sizes, columns of the projection row and mask / rotation constants of one attention layer"""
     _fields_ = [("H", C.c_int32), ("G", C.c_int32), ("D", C.c_int32), ("V", C.c_int32), ("q_col", C.c_int32), ("k_col", C.c_int32), ("v_col", C.c_int32),
                 ("gate_col", C.c_int32), ("scale", C.c_float), ("chunk", C.c_int32), ("window", C.c_int32), ("pool", C.c_int32), ("qk_eps", C.c_float),
-                ("rot_dims", C.c_int32), ("rot_freq", C.c_void_p), ("rot_scale", C.c_float), ("sink", C.c_void_p), ("latent_v", C.c_int32), ("gate", C.c_void_p), ("gate_ld", C.c_int64)]
+                ("rot_dims", C.c_int32), ("rot_freq", C.c_void_p), ("rot_scale", C.c_float), ("sink", C.c_void_p), ("latent_v", C.c_int32), ("gate", C.c_void_p), ("gate_ld", C.c_int64), ("ctx_rows", C.c_int32), ("kd", C.c_int32), ("kv_ld", C.c_int64), ("krot", C.c_void_p), ("krot_ld", C.c_int64)]
 
 
 class RetentionDesc(C.Structure):
@@ -85,6 +85,16 @@ def attn_desc(H: int, G: int, D: int, V: int, scale: float, *, values_from_keys:
     d = AttnDesc(H, G, D, V, 0, k_col, v_col, end if gated else -1, scale, chunk, window, pool, qk_eps, 2 * rot_freq.numel() if rot_freq is not None else 0,
                  rot_freq.data_ptr() if rot_freq is not None else None, rot_scale, sink.data_ptr() if sink is not None else None, 0)
     d.width = end + (H if gated else 0)
+    return d
+
+
+def expanded_attn_desc(H: int, Dn: int, Rd: int, V: int, scale: float, krot: torch.Tensor, *, gated: bool = True, sink: Optional[torch.Tensor] = None) -> "AttnDesc":
+    """descriptor of the attend step of a latent-attention layer over per-head keys and values that were projected out of the step's gathered
+    context: rows [H * Dn keys | H * V values]; the Rd rotated key dimensions of every head come from krot, a view [rows, Rd] of the paged pool"""
+    D = Dn + Rd
+    d = AttnDesc(H, H, D, V, 0, 0, H * Dn, 0 if gated else -1, scale, 0, 0, 0, -1.0, 0, None, 1.0, sink.data_ptr() if sink is not None else None, 0, None, 0,
+                 1, Dn if Rd > 0 else 0, H * (Dn + V), krot.data_ptr() if Rd > 0 else None, krot.stride(-2) if Rd > 0 else 0)
+    d.width = H * D
     return d
 
 
@@ -346,14 +356,26 @@ def moe_sort(ids: torch.Tensor, pairs: int, E: int, counts: torch.Tensor, offs: 
 
 @_timed
 def moe_linear(x: torch.Tensor, x_div: int, w: torch.Tensor, ids: torch.Tensor, order: Optional[torch.Tensor], offs: Optional[torch.Tensor], pairs: int, act: int,
-               out: torch.Tensor):
-    """one projection of every (token, choice) pair through its expert's weight; w bf16 [E, N, K]; out [pairs, N] (f32 when act is ACT_NONE)"""
+               out: torch.Tensor, limit: float = 0.0, alpha: float = 0.0, shift: float = 0.0):
+    """one projection of every (token, choice) pair through its expert's weight; w bf16 [E, N, K]; out [pairs, N] (f32 when act is ACT_NONE);
+    gated kinds: the rows of every expert's weight alternate (gate j, up j) and out is [pairs, N / 2]"""
     _, K, ldx = _rows2d(x)
-    _, N, ldo = _rows2d(out)
-    E = w.shape[0]
-    assert w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape[1:]) == (N, K) and out.shape[0] >= pairs
-    _check(lib().b200seq_moe_linear(_p(x), _DT[x.dtype], C.c_int64(ldx), x_div, _p(w), _p(ids), _p(order), _p(offs), pairs, E, N, K, act, _p(out), _DT[out.dtype],
-                                    C.c_int64(ldo), _st(x)))
+    _, No, ldo = _rows2d(out)
+    E, N = w.shape[0], w.shape[1]
+    assert w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[2] == K and out.shape[0] >= pairs and No == (N // 2 if act in ACT_GATED else N)
+    _check(lib().b200seq_moe_linear_act(_p(x), _DT[x.dtype], C.c_int64(ldx), x_div, _p(w), _p(ids), _p(order), _p(offs), pairs, E, N, K, act, C.c_float(limit),
+                                        C.c_float(alpha), C.c_float(shift), _p(out), _DT[out.dtype], C.c_int64(ldo), _st(x)))
+
+
+@_timed
+def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ocol: int, act: int = ACT_NONE):
+    """out[t, h * ocol + n] = w[h, n] . x[t, h * K : (h + 1) * K] for every head: x [T, >= H * K] rows, w bf16 [H, N, K], out [T, >= (H - 1) * ocol + N] rows
+    (f32 when act is ACT_NONE, else a plain kind - ACT_IDENT: the product itself - in out's type)"""
+    T, _, ldx = _rows2d(x)
+    _, _, ldo = _rows2d(out)
+    H, N, K = w.shape
+    assert w.dtype == torch.bfloat16 and w.is_contiguous() and out.shape[0] == T and (act != ACT_NONE or out.dtype == torch.float32)
+    _check(lib().b200seq_head_linear(_p(x), _DT[x.dtype], C.c_int64(ldx), _p(w), T, H, N, K, act, _p(out), _DT[out.dtype], C.c_int64(ldo), C.c_int64(ocol), _st(x)))
 
 
 @_timed
@@ -402,13 +424,21 @@ def attn(qkvg: torch.Tensor, step: "StepDesc", kpool: torch.Tensor, vpool: torch
 
 @_timed
 def latent_prep(proj: torch.Tensor, c_col: int, gate_col: int, q: torch.Tensor, step: "StepDesc", H: int, Dn: int, Rd: int, R: int, norm_w: torch.Tensor, eps: float,
-                rot_freq: Optional[torch.Tensor], rot_scale: float, kpool: torch.Tensor, Qp: torch.Tensor, qn: torch.Tensor):
+                rot_freq: Optional[torch.Tensor], rot_scale: float, kpool: torch.Tensor, Qp: Optional[torch.Tensor], qn: Optional[torch.Tensor]):
+    """Qp and qn None: the rotated part of every query head turns in place in q (the step attends over per-head keys)"""
     _, _, ldp = _rows2d(proj)
     _, _, ldq = _rows2d(q)
-    _, _, ldQ = _rows2d(Qp)
-    assert qn.is_contiguous() and kpool.is_contiguous() and kpool.shape[-1] == R + Rd
+    ldQ = _rows2d(Qp)[2] if Qp is not None else 0
+    assert (qn is None or qn.is_contiguous()) and kpool.is_contiguous() and kpool.shape[-1] == R + Rd
     _check(lib().b200seq_latent_prep(_p(proj), C.c_int64(ldp), c_col, gate_col, _p(q), C.c_int64(ldq), C.byref(step), H, Dn, Rd, R, _p(norm_w), C.c_float(eps),
-                                     _p(rot_freq), C.c_float(rot_scale), _p(kpool), _p(Qp), C.c_int64(ldQ), _p(qn), _DT[qn.dtype], _st(proj)))
+                                     _p(rot_freq), C.c_float(rot_scale), _p(kpool), _p(Qp), C.c_int64(ldQ), _p(qn), _DT[qn.dtype] if qn is not None else F32, _st(proj)))
+
+
+@_timed
+def latent_gather(kpool: torch.Tensor, step: "StepDesc", R: int, ctx_rows: int, out: torch.Tensor):
+    """out[r] = the latent (first R floats) of the r-th (entry, position) of the step's contexts, from the paged pool, in out's type"""
+    assert kpool.is_contiguous() and out.is_contiguous() and out.shape[0] >= ctx_rows and out.shape[1] == R
+    _check(lib().b200seq_latent_gather(_p(kpool), C.c_int64(kpool.shape[-1]), C.byref(step), R, ctx_rows, _p(out), _DT[out.dtype], _st(kpool)))
 
 
 @_timed

@@ -185,6 +185,13 @@ typedef struct b200seq_attn_desc {
     int32_t latent_v;   /* attend: 1 = the values are the first V floats of the (single) key head's pool rows, vpool is not read (G == 1, V <= D) */
     const float* gate;  /* attend: when not null (and gate_col >= 0) the gate logit of (t, h) is gate[t * gate_ld + h] instead of the query row's */
     int64_t gate_ld;
+    int32_t ctx_rows;   /* attend: 1 = kpool / vpool hold the step's gathered context instead of pages: the rows of entry 0's positions 0 .. pos0 + len - 1,
+                           then entry 1's, ... (b200seq_latent_gather's order) */
+    int32_t kd;         /* attend: 0 < kd < D: only the first kd floats of a key head lie in kpool (head g at g * kd); the other D - kd are one part
+                           shared by all heads, read from krot's PAGED rows: krot[(page row) * krot_ld + (d - kd)] */
+    int64_t kv_ld;      /* attend: > 0: floats per position row of kpool and of vpool (default G * D and G * V) */
+    const float* krot;
+    int64_t krot_ld;
 } b200seq_attn_desc;
 int b200seq_attn_prep_ex(float* proj, int64_t ld, const b200seq_step* st, const b200seq_attn_desc* d, float* kpool, float* vpool, float* kpooled, float* vpooled,
                          void* stream);
@@ -203,6 +210,20 @@ int b200seq_attn_ex(const float* proj, int64_t ld, const b200seq_step* st, const
 int b200seq_latent_prep(const float* proj, int64_t ldp, int c_col, int gate_col, const float* q, int64_t ldq, const b200seq_step* st, int H, int Dn, int Rd, int R,
                         const float* norm_w, float eps, const float* rot_freq, float rot_scale, float* kpool, float* Qp, int64_t ldQ, void* qn, int qn_dtype,
                         void* stream);
+/* Steps of prompt portions attend over per-head keys instead (fewer operations per key than in the latent space): Qp == qn == null makes
+ * latent_prep turn the rotated part of every query head IN PLACE in q; b200seq_latent_gather then copies the latents of every position of
+ * every entry's context (0 .. pos0 + len - 1, entry after entry: ctx_rows rows in all) out of the pages into out [ctx_rows, R] in out_dtype,
+ * one projection of those rows gives per-head keys and values, and b200seq_attn_ex runs with ctx_rows = 1, kd = the unrotated key size and
+ * krot = the pool's rotated part.  Both forms give the same result up to rounding. */
+int b200seq_latent_gather(const float* kpool, int64_t kld, const b200seq_step* st, int R, int ctx_rows, void* out, int out_dtype, void* stream);
+
+/* ---- per-head projections ------------------------------------------------------------------------------------------------------------------
+ * out[t][h * ocol + n] = sum_k x[t][h * K + k] * w[h][n][k] for every token t < T and head h < H: x rows (f32 or bf16, stride ldx) hold the heads'
+ * inputs side by side, w is bf16 [H][N][K], out rows (stride ldo) hold the heads' results at a pitch of ocol >= N columns.  act: -1 the f32
+ * product; a plain kind (B200SEQ_ACT_IDENT: the product itself) written in out_dtype.  Few (token, head) pairs: the weights are streamed per
+ * pair; many tokens: tcgen05 tiles per head (bf16 rows, K % 8 == 0, 16-byte aligned) or exact f32 fma tiles. */
+int b200seq_head_linear(const void* x, int x_dtype, int64_t ldx, const void* w_bf16, int T, int H, int N, int K, int act, void* out, int out_dtype, int64_t ldo,
+                        int64_t ocol, void* stream);
 
 /* ---- rotary positions on head vectors inside projection rows -------------------------------------------------------------------------------
  * x[t][col + h * D + ..], h < nheads: the first rot_dims dimensions of every head turn by pos * freq[i]; pair (i, i + rot_dims / 2) when
@@ -267,6 +288,10 @@ int b200seq_moe_sort(const int32_t* ids, int pairs, int E, const int32_t* counts
  * result).  act: -1 none (out f32) or a plain activation kind (out in out_dtype).  out [pairs, N], stride ldo. */
 int b200seq_moe_linear(const void* x, int x_dtype, int64_t ldx, int x_div, const void* w_bf16, const int32_t* ids, const int32_t* sorted, const int32_t* offs,
                        int pairs, int E, int N, int K, int act, void* out, int out_dtype, int64_t ldo, void* stream);
+/* The same with any activation kind: gated kinds take expert weights [E][N][K] whose rows alternate (gate j, up j) and give out [pairs, N / 2]
+ * in out_dtype (limit / alpha / shift as in B200SEQ_ACT_SWISH_CLAMP); the gate | up product never reaches memory. */
+int b200seq_moe_linear_act(const void* x, int x_dtype, int64_t ldx, int x_div, const void* w_bf16, const int32_t* ids, const int32_t* sorted, const int32_t* offs,
+                           int pairs, int E, int N, int K, int act, float limit, float alpha, float shift, void* out, int out_dtype, int64_t ldo, void* stream);
 /* out[r] = x[sorted[r] / x_div] for every sorted pair r (bf16 rows of K): the tokens' activations in sorted order, so that the tensor-core
  * tiles of b200seq_moe_linear (sorted rows, x_div = 0, bf16, K % 8 == 0, 16-byte aligned rows, >= 32 pairs) can fetch them. */
 int b200seq_moe_gather(const void* x_bf16, int64_t ldx, const int32_t* sorted, int x_div, int pairs, int K, void* out_bf16, int64_t ldo, void* stream);

@@ -154,9 +154,10 @@ def table_experts(h: torch.Tensor, tokens: List[int], w: Dict[str, torch.Tensor]
 
 
 # ---- the model ---------------------------------------------------------------------------------------------------------------------------
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None) -> torch.Tensor:
-    """logits [T, vocab] of one sequence; layers_out collects the residual after every layer"""
-    w = {k: (v.double() if v.is_floating_point() else v) for k, v in w.items()}
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None, dtype=torch.float64) -> torch.Tensor:
+    """logits [T, vocab] of one sequence; layers_out collects the residual after every layer.  dtype float32 shows how far plain 32-bit
+    rounding alone moves the result of a configuration (some are ill-conditioned: a unit norm over a single value, for instance)"""
+    w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps, alpha = cfg["norm"]["eps"], cfg["postln_alpha"]
     x = w["embed"][torch.tensor(tokens)]
     for i, lay in enumerate(cfg["layers"]):

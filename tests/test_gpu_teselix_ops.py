@@ -229,8 +229,9 @@ def latent_reference(kv, q, uk, uv, norm_w, sink, gate, H, Dn, Rd, V, R, scale, 
     return (o * torch.sigmoid(gate.double())[:, :, None]).reshape(T, H * V)
 
 
-def run_latent(ops, kv, q, gate, uk, uv, norm_w, sink, H, Dn, Rd, V, R, scale, eps, rot, plan, pages, kpool, act=torch.float32):
-    """plan: steps of [(name, n)]; kv / q / gate: name -> whole-sequence tensors; pages: name -> block table; returns name -> [T, H * V]"""
+def run_latent(ops, kv, q, gate, uk, uv, norm_w, sink, H, Dn, Rd, V, R, scale, eps, rot, plan, pages, kpool, act=torch.float32, expanded=False):
+    """plan: steps of [(name, n)]; kv / q / gate: name -> whole-sequence tensors; pages: name -> block table; returns name -> [T, H * V].
+    expanded: steps that are not all single tokens gather their contexts' latents, project per-head keys | values and attend over those"""
     from blazr_b200.layered import RotarySpec
     fr, amp = RotarySpec(Rd, rot["base"], None, "interleaved").table()
     fr = torch.from_numpy(fr).to(DEV)
@@ -244,19 +245,34 @@ def run_latent(ops, kv, q, gate, uk, uv, norm_w, sink, H, Dn, Rd, V, R, scale, e
         T = sum(k for _, k in step)
         proj = torch.cat([torch.cat([kv[n][fed[n]:fed[n] + k], gate[n][fed[n]:fed[n] + k]], 1) for n, k in step]).to(DEV)
         qq = torch.cat([q[n][fed[n]:fed[n] + k] for n, k in step]).to(DEV)
+        if expanded and T > len(step):
+            ops.latent_prep(proj, 0, -1, qq, st, H, Dn, Rd, R, norm_w.to(DEV), eps, fr, amp, kpool, None, None)
+            ctx = sum(fed[n] + k for n, k in step)
+            cx, kvx = torch.empty(ctx, R, device=DEV, dtype=act), torch.empty(ctx, H * (Dn + V), device=DEV)
+            ops.latent_gather(kpool, st, R, ctx, cx)
+            ops.linear(cx, torch.cat([uk, uv]).bfloat16().to(DEV), kvx)
+            dx = ops.expanded_attn_desc(H, Dn, Rd, V, scale, kpool.view(-1, R + Rd)[:, R:], gated=True, sink=sink)
+            up = torch.empty(T, H * V, device=DEV, dtype=act)
+            scratch = torch.empty(max(1, ops.attn_scratch_floats(T, len(step), H, H, V, 1024)), device=DEV)
+            ops.attn_ex(qq, st, dx, kvx, kvx[:, H * Dn:], up, scratch, gate=proj[:, R + Rd:])
+            o0 = 0
+            for n, k in step:
+                outs[n].append(up[o0:o0 + k].float().cpu())
+                o0 += k
+                fed[n] += k
+            continue
         Qp = torch.zeros(T, H * (R + Rd), device=DEV)
-        qn = torch.empty(T * H, Dn, device=DEV, dtype=act)
+        qn = torch.empty(T, H * Dn, device=DEV, dtype=act)
         ops.latent_prep(proj, 0, -1, qq, st, H, Dn, Rd, R, norm_w.to(DEV), eps, fr, amp, kpool, Qp, qn)
-        ids = (torch.arange(T * H, dtype=torch.int32) % H).to(DEV)
-        ops.moe_linear(qn, 0, ukT, ids, None, None, T * H, ops.ACT_NONE, Qp.view(T * H, R + Rd)[:, :R])
+        ops.head_linear(qn, ukT, Qp, R + Rd)
         o = torch.empty(T, H * R, device=DEV, dtype=act)
         scratch = torch.empty(max(1, ops.attn_scratch_floats(T, len(step), H, 1, R, 1024)), device=DEV)
         ops.attn_ex(Qp, st, desc, kpool, None, o, scratch, gate=proj[:, R + Rd:])
-        up = torch.empty(T * H, V, device=DEV, dtype=act)
-        ops.moe_linear(o.view(T * H, R), 0, uvh, ids, None, None, T * H, ops.ACT_IDENT, up)
+        up = torch.empty(T, H * V, device=DEV, dtype=act)
+        ops.head_linear(o, uvh, up, V, ops.ACT_IDENT)
         o0 = 0
         for n, k in step:
-            outs[n].append(up.view(T, H * V)[o0:o0 + k].float().cpu())
+            outs[n].append(up[o0:o0 + k].float().cpu())
             o0 += k
             fed[n] += k
     return {n: torch.cat(v) for n, v in outs.items()}
@@ -275,10 +291,12 @@ def test_latent_attention_over_scattered_and_reused_pages(ops, H, Dn, Rd, V, R):
     pages = {"a": perm[:6], "b": perm[6:9], "c": perm[:5]}
     ref = {n: latent_reference(kv, q, uk, uv, norm_w, sink.cpu(), g, H, Dn, Rd, V, R, scale, eps, rot) for n, (kv, q, g) in seqs.items()}
     plan = [[("a", 20), ("b", 1)], [("b", 2), ("a", 1)], [("a", 47), ("b", 30)], [("a", 1), ("b", 1)], [("a", 21), ("b", 3)], [("c", 2)], [("c", 67)], [("c", 1)]]
-    got = run_latent(ops, {n: s[0] for n, s in seqs.items()}, {n: s[1] for n, s in seqs.items()}, {n: s[2] for n, s in seqs.items()}, uk, uv, norm_w, sink, H, Dn, Rd, V, R,
-                     scale, eps, rot, plan, pages, kpool)
-    for n in seqs:
-        close(got[n], ref[n], 2e-5)
+    for expanded in (False, True):      # in the latent space throughout; per-head keys for the steps with portions
+        kpool.fill_(50.0)
+        got = run_latent(ops, {n: s[0] for n, s in seqs.items()}, {n: s[1] for n, s in seqs.items()}, {n: s[2] for n, s in seqs.items()}, uk, uv, norm_w, sink, H, Dn, Rd, V, R,
+                         scale, eps, rot, plan, pages, kpool, expanded=expanded)
+        for n in seqs:
+            close(got[n], ref[n], 2e-5)
     assert ops.error_flags() == 0
 
 
@@ -305,9 +323,11 @@ def test_latent_attention_finds_a_far_key_and_counts_the_sink_once(ops):
             assert 0.02 < ref[595, :V].norm().item() / c7.norm().item() < 0.9
         kpool = torch.zeros(40, 16, R + Rd, device=DEV)
         plan = [[("a", 580)], [("a", 13)]] + [[("a", 1)]] * 7
-        got = run_latent(ops, {"a": kv}, {"a": q}, {"a": gate}, uk, uv, norm_w, sink, H, Dn, Rd, V, R, scale, eps, rot, plan, {"a": list(range(39, 1, -1))}, kpool)
-        close(got["a"][580:], ref[580:], 3e-5)
-        close(got["a"][:580], ref[:580], 3e-5)
+        for expanded in (False, True):
+            got = run_latent(ops, {"a": kv}, {"a": q}, {"a": gate}, uk, uv, norm_w, sink, H, Dn, Rd, V, R, scale, eps, rot, plan, {"a": list(range(39, 1, -1))}, kpool,
+                             expanded=expanded)
+            close(got["a"][580:], ref[580:], 3e-5)
+            close(got["a"][:580], ref[:580], 3e-5)
 
 
 def test_bfloat16_activations_in_latent_attention(ops):
@@ -316,9 +336,10 @@ def test_bfloat16_activations_in_latent_attention(ops):
     uk, uv = rnd(H * Dn, R, seed=83, scale=R ** -0.5).bfloat16().float(), rnd(H * V, R, seed=84, scale=R ** -0.5).bfloat16().float()
     norm_w, sink = 1 + rnd(R, seed=85, scale=0.1), rnd(H, seed=86).to(DEV)
     ref = latent_reference(kv, q, uk, uv, norm_w, sink.cpu(), gate, H, Dn, Rd, V, R, scale, eps, rot)
-    got = run_latent(ops, {"a": kv}, {"a": q}, {"a": gate}, uk, uv, norm_w, sink, H, Dn, Rd, V, R, scale, eps, rot, [[("a", 70)]] + [[("a", 1)]] * 10, {"a": pages_for(80)},
-                     torch.zeros(8, 16, R + Rd, device=DEV), act=torch.bfloat16)
-    close(got["a"], ref, 3e-2)
+    for expanded in (False, True):
+        got = run_latent(ops, {"a": kv}, {"a": q}, {"a": gate}, uk, uv, norm_w, sink, H, Dn, Rd, V, R, scale, eps, rot, [[("a", 70)]] + [[("a", 1)]] * 10, {"a": pages_for(80)},
+                         torch.zeros(8, 16, R + Rd, device=DEV), act=torch.bfloat16, expanded=expanded)
+        close(got["a"], ref, 3e-2)
 
 
 # ---- experts ---------------------------------------------------------------------------------------------------------------------------------
@@ -349,14 +370,22 @@ def test_table_choice_and_gated_experts(ops, T, E, top, ff, W, act):
     assert torch.equal(ids.cpu().view(T, top), table[tok.long()]) and bool((wts == 1.0 / top).all())
     assert torch.equal(cnt.cpu(), torch.bincount(table[tok.long()].flatten(), minlength=E).to(torch.int32))
     z2, mid, ys = torch.empty(pairs, 2 * ff, device=DEV), torch.empty(pairs, ff, device=DEV, dtype=act), torch.empty(pairs, W, device=DEV)
+    mid2 = torch.empty(pairs, ff, device=DEV, dtype=act)
     if pairs <= 64:
         order = offs = slot = None
-        ops.moe_linear(xd, top, w_up, ids, None, None, pairs, ops.ACT_NONE, z2)
     else:
         order, offs, slot = torch.empty(pairs, **i32), torch.zeros(E + 1, **i32), torch.empty(pairs, **i32)
         ops.moe_sort(ids, pairs, E, cnt, offs, order, slot)
-        ops.moe_linear(xd, top, w_up, ids, order, offs, pairs, ops.ACT_NONE, z2)
-    ops.act(z2, ops.ACT_SWISH_CLAMP, mid, limit, 1.702, 1.0)
+    ops.moe_linear(xd, top, w_up, ids, order, offs, pairs, ops.ACT_NONE, z2)               # product, then the activation ...
+    ops.act(z2, ops.ACT_SWISH_CLAMP, mid2, limit, 1.702, 1.0)
+    ops.moe_linear(xd, top, w_up, ids, order, offs, pairs, ops.ACT_SWISH_CLAMP, mid, limit, 1.702, 1.0)     # ... and both in one kernel
+    close(mid.float(), mid2.float().cpu(), 1e-6 if act == torch.float32 else 1e-2)
+    if order is not None and act == torch.bfloat16:      # rows in sorted order: the tensor-core tiles with the gated epilogue
+        xs = torch.empty(pairs, W, device=DEV, dtype=act)
+        ops.moe_gather(xd, top, order, pairs, xs)
+        mid3 = torch.empty(pairs, ff, device=DEV, dtype=act)
+        ops.moe_linear(xs, 0, w_up, ids, order, offs, pairs, ops.ACT_SWISH_CLAMP, mid3, limit, 1.702, 1.0)
+        close(mid3.float(), mid2.float().cpu(), 2e-2)
     ops.moe_linear(mid, 0, w_down, ids, order, offs, pairs, ops.ACT_NONE, ys)
     smid, sh = torch.empty(T, 16, device=DEV, dtype=act), torch.empty(T, W, device=DEV)
     if T <= 8 or act == torch.bfloat16:
@@ -370,6 +399,25 @@ def test_table_choice_and_gated_experts(ops, T, E, top, ff, W, act):
     ops.moe_combine(ys, wts, slot, T, top, sh, None, y)
     close(y, ref, 2e-5 if act == torch.float32 else 2e-2)
     assert ops.error_flags() == 0
+
+
+@pytest.mark.parametrize("T,H,N,K,xdt", [(3, 5, 7, 9, torch.float32), (2, 20, 16, 24, torch.bfloat16), (40, 3, 10, 6, torch.float32), (100, 4, 24, 16, torch.bfloat16),
+                                         (300, 6, 136, 72, torch.bfloat16), (70, 2, 200, 64, torch.float32), (17, 4, 8, 8, torch.bfloat16)])
+def test_per_head_projections(ops, T, H, N, K, xdt):
+    """every head's slice of a row through that head's own weight: per-pair rows, exact tiles, tensor-core tiles per head; results at a pitch
+    wider than N, columns between the heads' results untouched"""
+    x = rnd(T, H * K + 8, seed=97).to(xdt)
+    w = rnd(H, N, K, seed=98, scale=K ** -0.5).bfloat16()
+    ref = torch.einsum("thk,hnk->thn", x[:, :H * K].double().view(T, H, K), w.double())
+    pitch = N + 3
+    out = torch.full((T, H * pitch + 2), 7.0, device=DEV)
+    ops.head_linear(x.to(DEV)[:, :H * K], w.to(DEV), out, pitch)
+    got = out[:, :H * pitch].view(T, H, pitch)
+    close(got[:, :, :N], ref, 2e-6 if xdt == torch.float32 else 1e-5)
+    assert bool((got[:, :, N:] == 7.0).all()) and bool((out[:, H * pitch:] == 7.0).all())
+    ob = torch.empty(T, H * N, device=DEV, dtype=torch.bfloat16)
+    ops.head_linear(x.to(DEV)[:, :H * K], w.to(DEV), ob, N, ops.ACT_IDENT)
+    close(ob.float().view(T, H, N), ref, 6e-3)
 
 
 def test_projection_written_in_the_activation_type(ops):
