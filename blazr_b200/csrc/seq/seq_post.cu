@@ -89,6 +89,99 @@ __global__ void post_norm_kernel(const PostArgs a, const b200seq_step st) {
     }
 }
 
+// The same with the row held in registers (W <= 4 * EPT * blockDim.x, W % 4 == 0, 16-byte accesses): a thread owns EPT pieces of four
+// neighbouring elements.  PRE (steps of few rows, bound by latency): every input of the thread's pieces, the norm's weights and the next
+// shift's operands included, is requested before the first is used, so a block pays one round trip to memory instead of one per pass.
+// Without PRE (many rows, bound by bandwidth) only the sum is kept and the small per-column vectors are read where they are used.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void store_act4(void* out, int dtype, int64_t idx, const float4 v) {
+    if (dtype == B200SEQ_F32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + idx) = v;
+    } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&lo), u.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + idx) = u;
+    }
+}
+template <int EPT, bool PRE>
+__global__ void post_norm_reg_kernel(const PostArgs a, const b200seq_step st) {
+    __shared__ float red[40];
+    const int r = blockIdx.x;
+    const int64_t t = a.rows ? a.rows[r] : r;
+    const int W = a.W, nt = blockDim.x;
+    int e = -1;
+    bool last = false;
+    if (a.state_out || a.next_mu) {
+        e = st.tok_ent[t];
+        last = t + 1 == st.ent_start[e + 1];
+    }
+    const float* prev = nullptr;
+    if (a.next_mu && st.ent_pos0[e] != 0) prev = a.next_state + (int64_t)st.ent_slot[e] * W;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 v[EPT], wv[PRE ? EPT : 1], bv[PRE ? EPT : 1], mu[PRE ? EPT : 1], pv[PRE ? EPT : 1];
+    float4 xv[EPT], yv[EPT], zv[EPT], gv[EPT];
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+        const int i = (threadIdx.x + k * nt) * 4;
+        const bool in = i < W;
+        xv[k] = in ? ld4(a.x + t * W + i) : zero;
+        yv[k] = (in && a.y) ? ld4(a.y + t * W + i) : zero;
+        zv[k] = (in && a.zg) ? ld4(a.zg + t * a.ldz + i) : zero;
+        gv[k] = (in && a.gate_b) ? ld4(a.gate_b + i) : zero;
+        if (PRE) {
+            wv[k] = in ? ld4(a.w + i) : zero;
+            bv[k] = (in && a.b) ? ld4(a.b + i) : zero;
+            mu[k] = (in && a.next_mu) ? ld4(a.next_mu + i) : zero;
+            pv[k] = (in && prev) ? ld4(prev + i) : zero;
+        }
+    }
+    float part = 0.f;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+        const int i = (threadIdx.x + k * nt) * 4;
+        v[k] = xv[k];
+        if (a.y) {
+            const bool g = a.zg != nullptr;
+            v[k].x = fmaf(a.alpha, xv[k].x, (g ? sigmoidf_acc(zv[k].x + gv[k].x) : 1.f) * yv[k].x);
+            v[k].y = fmaf(a.alpha, xv[k].y, (g ? sigmoidf_acc(zv[k].y + gv[k].y) : 1.f) * yv[k].y);
+            v[k].z = fmaf(a.alpha, xv[k].z, (g ? sigmoidf_acc(zv[k].z + gv[k].z) : 1.f) * yv[k].z);
+            v[k].w = fmaf(a.alpha, xv[k].w, (g ? sigmoidf_acc(zv[k].w + gv[k].w) : 1.f) * yv[k].w);
+        }
+        if (i >= W) v[k] = zero;
+        if (a.state_out && last && i < W) *reinterpret_cast<float4*>(a.state_out + (int64_t)st.ent_slot[e] * W + i) = xv[k];
+        part += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    const float mean = block_sum(part, red) / (float)W;
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+        if ((threadIdx.x + k * nt) * 4 < W) {
+            const float d0 = v[k].x - mean, d1 = v[k].y - mean, d2 = v[k].z - mean, d3 = v[k].w - mean;
+            sq = fmaf(d0, d0, sq), sq = fmaf(d1, d1, sq), sq = fmaf(d2, d2, sq), sq = fmaf(d3, d3, sq);
+        }
+    }
+    const float rinv = 1.0f / sqrtf(block_sum(sq, red) / (float)W + a.eps);
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+        const int i = (threadIdx.x + k * nt) * 4;
+        if (i >= W) continue;
+        const float4 w4 = PRE ? wv[k] : ld4(a.w + i);
+        const float4 b4 = PRE ? bv[k] : (a.b ? ld4(a.b + i) : zero);
+        float4 n;
+        n.x = fmaf((v[k].x - mean) * rinv, w4.x, b4.x), n.y = fmaf((v[k].y - mean) * rinv, w4.y, b4.y);
+        n.z = fmaf((v[k].z - mean) * rinv, w4.z, b4.z), n.w = fmaf((v[k].w - mean) * rinv, w4.w, b4.w);
+        if (a.x_out) *reinterpret_cast<float4*>(a.x_out + t * W + i) = n;
+        if (a.a_out) store_act4(a.a_out, a.out_dtype, (int64_t)r * W + i, n);
+        if (a.next_mu) {
+            const float4 m4 = PRE ? mu[k] : ld4(a.next_mu + i);
+            const float4 p4 = PRE ? pv[k] : (prev ? ld4(prev + i) : zero);
+            store_act4(a.a_shift_out, a.out_dtype, (int64_t)r * W + i,
+                       make_float4(fmaf(p4.x - n.x, m4.x, n.x), fmaf(p4.y - n.y, m4.y, n.y), fmaf(p4.z - n.z, m4.z, n.z), fmaf(p4.w - n.w, m4.w, n.w)));
+        }
+    }
+}
+
 }  // namespace b200seq
 
 using namespace b200seq;
@@ -119,7 +212,28 @@ extern "C" int b200seq_post_norm(const float* x, const float* y, const float* zg
         if (e != cudaSuccess) return cuda_status(e, "post_norm attribute");
     }
     b200seq_step none{};
-    post_norm_kernel<<<R, W >= 4096 ? 512 : (W >= 1024 ? 256 : 128), smem, (cudaStream_t)stream>>>(a, st ? *st : none);
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (W <= 8192 && W % 4 == 0 && ldz % 4 == 0 && al(x) && al(y) && al(zg) && al(gate_b) && al(w) && al(b) && al(x_out) && al(a_out) && al(state_out) && al(next_mu) &&
+        al(next_state) && al(a_shift_out)) {   // the row fits in registers, 16-byte accesses
+        const int q = W / 4;
+        const int nt = q <= 64 ? 64 : (q <= 128 ? 128 : (q <= 512 ? 256 : 512));
+        const int ept = (q + nt - 1) / nt;
+        const bool pre = R <= 64;
+        cudaStream_t cs = (cudaStream_t)stream;
+        const b200seq_step sd = st ? *st : none;
+#define POST_LAUNCH(E_)                                                            \
+    do {                                                                           \
+        if (pre) post_norm_reg_kernel<E_, true><<<R, nt, 0, cs>>>(a, sd);          \
+        else post_norm_reg_kernel<E_, false><<<R, nt, 0, cs>>>(a, sd);             \
+    } while (0)
+        if (ept <= 1) POST_LAUNCH(1);
+        else if (ept <= 2) POST_LAUNCH(2);
+        else POST_LAUNCH(4);
+#undef POST_LAUNCH
+        SEQ_LAUNCH_CHECK("post_norm");
+        return 0;
+    }
+    post_norm_kernel<<<R, 512, smem, (cudaStream_t)stream>>>(a, st ? *st : none);
     SEQ_LAUNCH_CHECK("post_norm");
     return 0;
 }

@@ -221,6 +221,14 @@ class _Workspace:
             self.moe_ys = torch.empty((cap * top, W), **f32)
             self.moe_sh = torch.empty((cap, W), **f32)
             self.moe_xs = torch.empty((cap * top, W), **act) if model.act_dtype == torch.bfloat16 else None   # tokens' rows in sorted pair order
+            # table-routed layers choose (and sort) at the start of the step, each into buffers of its own
+            self.route = {}
+            for i, L in enumerate(model.layers):
+                f = L["spec"].ff
+                if isinstance(f, MoeFfSpec) and f.router == "table":
+                    n = cap * f.top
+                    self.route[i] = dict(ids=torch.empty(n, **i32), wts=torch.empty(n, **f32), cnt=torch.zeros(f.experts, **i32), off=torch.zeros(f.experts + 1, **i32),
+                                         order=torch.empty(n, **i32), slot=torch.empty(n, **i32))
         self.scratch = torch.empty(max(1, model.scratch_floats(cap)), **f32)      # work area: segmented state-space scan, key-split attention
         self.next_ids = torch.empty((cap,), dtype=torch.int32, device=dev)
         # int32 step arrays in one buffer: ids | ent | pos | want | start | slot | pos0 | block_table
@@ -781,11 +789,38 @@ class LayeredModel:
         ops.embed_streams(self.embed, ws.view("ids"), cfg.embed_scale, x.view(T, 1, cfg.width))
         n = len(self.layers)
         single = T == B
+        # What does not lie on a sublayer's critical path runs beside it on other streams (inside a captured decode step: parallel branches of
+        # the graph): the residual gate's projection beside the mixer / the experts, the shared expert on a third stream, and - because a
+        # table-routed choice depends on the token ids alone - the choice and the sort of EVERY layer at the start of the step.
+        par = self.overlap_branches and self.dev.type == "cuda" and seqops.timeline is None
+        if par and self._side is None:
+            self._side, self._side2 = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+        main = torch.cuda.current_stream(self.dev) if par else None
+
+        def beside(stream, fn):
+            """fn on `stream` after what the main stream has queued so far; returns the event to wait for (None: it ran in line)"""
+            if not par:
+                fn()
+                return None
+            fork, done = torch.cuda.Event(), torch.cuda.Event()
+            fork.record(main)
+            stream.wait_event(fork)
+            with torch.cuda.stream(stream):
+                fn()
+                done.record(stream)
+            return done
+
+        def wait(ev):
+            if ev is not None:
+                main.wait_event(ev)
+
+        tabled = [i for i, L in enumerate(self.layers) if isinstance(L["spec"].ff, MoeFfSpec) and L["spec"].ff.router == "table"]
+        routed = beside(self._side2 if par else None, lambda: [self._table_route(self.layers[i], ws, i, T) for i in tabled]) if tabled else None
         if n:
             ops.token_shift(x, self.layers[0]["shift"], self.layers[0]["shift_state"], st, a, ash)
         for i, L in enumerate(self.layers):
             ls: LayerSpec = L["spec"]
-            ops.linear(a, L["rg1"], zg)
+            gate_done = beside(self._side, lambda: ops.linear(a, L["rg1"], zg))
             if ls.kind == "retention":
                 self._retention(L, ls.mixer, ws, st, T, ash, y)
             else:
@@ -793,10 +828,17 @@ class LayeredModel:
             close = dict(y=y, zg=zg, alpha=cfg.post_alpha, x_out=x, a_out=a, step=st)
             q = 1
             if ls.ff is not None:
+                wait(gate_done)
                 ops.post_norm(x, L["norm1"], L["norm1_b"], cfg.eps, gate_b=L["rg1_b"], state_out=L["shift_state"], **close)
-                ops.linear(a, L["rg2"], zg)
+                gate_done = beside(self._side, lambda: ops.linear(a, L["rg2"], zg))
                 if isinstance(ls.ff, MoeFfSpec):
-                    self._moe_ff(L, ls.ff, ws, T, a, y)
+                    shared_done = None
+                    if par and ls.ff.shared_ff:
+                        shared_done = beside(self._side2, lambda: self._shared_expert(L, ls.ff, ws, T, a))
+                    if i in tabled:
+                        wait(routed)
+                        routed = None
+                    self._moe_ff(L, ls.ff, ws, T, a, y, shared_done, route=ws.route.get(i))
                 else:
                     self._dense_ff(L, ls.ff, ws, T, a, y, inner=ws.ff_inner, proj=ws.ff_proj)
                 q = 2
@@ -805,11 +847,13 @@ class LayeredModel:
             nxt = self.layers[i + 1] if i + 1 < n else None
             if nxt is not None and single:
                 close.update(next_mu=nxt["shift"], next_state=nxt["shift_state"], a_shift_out=ash)
+            wait(gate_done)
             ops.post_norm(x, L[f"norm{q}"], L[f"norm{q}_b"], cfg.eps, gate_b=L[f"rg{q}_b"], **close)
             if nxt is not None and not single:
                 ops.token_shift(x, nxt["shift"], nxt["shift_state"], st, None, ash)
             if debug_layers is not None:
                 debug_layers.append(x.cpu())
+        wait(routed)
         if R:
             ops.post_norm(x, self.final_norm, self.final_bias, cfg.eps, rows=ws.view("want")[:R], a_out=ws.fin[:R])
 
@@ -925,48 +969,63 @@ class LayeredModel:
             seqops.linear(a, w, z)
             seqops.act(z, kind, out, limit, alpha, shift)
 
+    def _table_route(self, L, ws: _Workspace, i: int, T: int) -> None:
+        """choice (and, for many pairs, the sort by expert) of layer i's table-routed experts into the layer's own buffers: it needs the token ids only"""
+        f, r = L["spec"].ff, ws.route[i]
+        pairs = T * f.top
+        rows_form = pairs <= self.MOE_ROW_PAIRS
+        seqops.moe_table_route(L["table"], ws.view("ids"), T, f.experts, f.top, r["ids"], r["wts"], None if rows_form else r["cnt"])
+        if not rows_form:
+            seqops.moe_sort(r["ids"], pairs, f.experts, r["cnt"], r["off"], r["order"], r["slot"])
+
     MOE_ROW_PAIRS = 64      # up to this many (token, choice) pairs the experts' weights are streamed per pair; more: tiles over sorted pairs
 
-    def _moe_ff(self, L, f: "MoeFfSpec", ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor, shared_done=None) -> None:
-        """shared_done: event after which the shared expert's output is in ws.moe_sh (it ran elsewhere); None: it runs here"""
+    def _moe_ff(self, L, f: "MoeFfSpec", ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor, shared_done=None, route=None) -> None:
+        """shared_done: event after which the shared expert's output is in ws.moe_sh (it ran elsewhere); None: it runs here.
+        route: the layer's own choice buffers, filled (and sorted) earlier in the step (table-routed layers); None: the choice is made here"""
         ops = seqops
         E, top = f.experts, f.top
         gated_shared = bool(f.shared_ff and f.shared_gate)
         pairs = T * top
         rows_form = pairs <= self.MOE_ROW_PAIRS
         z = None
-        if f.router == "table":         # no router: the token id names the experts
-            ops.moe_table_route(L["table"], ws.view("ids"), T, E, top, ws.moe_ids, ws.moe_wts, None if rows_form else ws.moe_cnt)
+        ids, wts = (route["ids"], route["wts"]) if route is not None else (ws.moe_ids, ws.moe_wts)
+        if route is not None:
+            pass
+        elif f.router == "table":         # no router: the token id names the experts
+            ops.moe_table_route(L["table"], ws.view("ids"), T, E, top, ids, wts, None if rows_form else ws.moe_cnt)
         else:
             z = ws.moe_z[:T, :L["w_router"].shape[0]]
             if T <= 8 and rows_form:        # few tokens: projection and choice in one kernel
-                ops.moe_router(a, L["w_router"], E, f.groups, f.keep, top, z, ws.moe_ids, ws.moe_wts)
+                ops.moe_router(a, L["w_router"], E, f.groups, f.keep, top, z, ids, wts)
             else:
                 ops.linear(a, L["w_router"], z)
-                ops.moe_route(z, E, f.groups, f.keep, top, ws.moe_ids, ws.moe_wts, None if rows_form else ws.moe_cnt)
+                ops.moe_route(z, E, f.groups, f.keep, top, ids, wts, None if rows_form else ws.moe_cnt)
         kind = ops.ACT_KINDS[f.act]
         mid = ws.moe_act.view(-1)[:pairs * f.ff].view(pairs, f.ff)
         act_args = (f.limit, f.alpha, f.up_shift) if kind in ops.ACT_GATED else ()     # gated experts: activation of the (gate, up) pairs in the projection's epilogue
         ys = ws.moe_ys[:pairs]
         if rows_form:
             order = offs = slot = None
+        elif route is not None:
+            order, offs, slot = route["order"], route["off"], route["slot"]
         else:
             order, offs, slot = ws.moe_order, ws.moe_off, ws.moe_slot
-            ops.moe_sort(ws.moe_ids, pairs, E, ws.moe_cnt, offs, order, slot)
+            ops.moe_sort(ids, pairs, E, ws.moe_cnt, offs, order, slot)
         if not rows_form and ws.moe_xs is not None and ops.tc_usable(a, a.shape[1]) and f.ff % 8 == 0:
             xs = ws.moe_xs[:pairs]                  # tensor-core tiles fetch contiguous rows: put the tokens' rows in sorted order first
             ops.moe_gather(a, top, order, pairs, xs)
-            ops.moe_linear(xs, 0, L["w_eup"], ws.moe_ids, order, offs, pairs, kind, mid, *act_args)
+            ops.moe_linear(xs, 0, L["w_eup"], ids, order, offs, pairs, kind, mid, *act_args)
         else:
-            ops.moe_linear(a, top, L["w_eup"], ws.moe_ids, order, offs, pairs, kind, mid, *act_args)
-        ops.moe_linear(mid, 0, L["w_edown"], ws.moe_ids, order, offs, pairs, ops.ACT_NONE, ys)
+            ops.moe_linear(a, top, L["w_eup"], ids, order, offs, pairs, kind, mid, *act_args)
+        ops.moe_linear(mid, 0, L["w_edown"], ids, order, offs, pairs, ops.ACT_NONE, ys)
         sh = None
         if shared_done is not None:
             torch.cuda.current_stream(self.dev).wait_event(shared_done)
             sh = ws.moe_sh[:T]
         elif f.shared_ff:
             sh = self._shared_expert(L, f, ws, T, a)
-        ops.moe_combine(ys, ws.moe_wts, slot, T, top, sh, z[:, E] if gated_shared and z is not None else None, y)
+        ops.moe_combine(ys, wts, slot, T, top, sh, z[:, E] if gated_shared and z is not None else None, y)
 
     def _shared_expert(self, L, f: "MoeFfSpec", ws: _Workspace, T: int, a: torch.Tensor) -> torch.Tensor:
         smid = ws.ff_inner.view(-1)[:T * f.shared_ff].view(T, f.shared_ff)

@@ -230,6 +230,13 @@ def _cost(name: str, shapes, scal, scen: dict, kw: dict = None):
         if scen["prefill"]:
             flops += 2.0 * T * d.H * 32 * (d.D + d.V)                                       # on average 32 of the chunk's 64 keys are at or before a token
         return T * (ld * 4 + d.H * d.V * sh[2][1]) + 2 * B * d.H * d.D * d.V * 4, flops, "f32" if scen["prefill"] else "hbm"
+    if name == "latent_gather":   # pool rows in, latents out in the activation type
+        (rows, R), es = sh[-1][0], sh[-1][1]
+        return rows * R * (4 + es), 0.0, "hbm"
+    if name == "head_linear":     # x, w [H, N, K], out
+        (xs, xe), (ws, _), (os_, oe) = sh[0], sh[1], sh[2]
+        H, N, K = ws
+        return xs[0] * H * K * xe + H * N * K * 2 + xs[0] * H * N * oe, 2.0 * xs[0] * H * N * K, "tensor"
     if name == "latent_prep":     # projection row and query row in, pool row, rotated query parts and unrotated parts out
         (T, ldp), (_, ldq) = sh[0][0], sh[1][0]
         return T * (ldp + 2 * ldq) * 4, 0.0, "hbm"
@@ -369,8 +376,9 @@ def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, ba
     if gem:     # window of `chunk` positions plus one pooled entry per block of 16 wholly before it
         vis = np.minimum(pos + 1, chunk) + np.maximum(0, (pos - chunk + 1) // pool)
         scen = dict(prefill=True, entries=1, visible_keys=int(vis.sum()), kv_rows_touched=S + S // pool, attn_desc=desc0)
-    elif tes:   # every earlier position
-        scen = dict(prefill=True, entries=1, visible_keys=int((pos + 1).sum()), kv_rows_touched=S, attn_desc=desc0, ret_desc=rdesc0)
+    elif tes:   # every earlier position; a step of portions attends over per-head keys projected from the gathered latents
+        descx = next((L["desc_x"] for L in model.layers if "desc_x" in L), desc0)
+        scen = dict(prefill=True, entries=1, visible_keys=int((pos + 1).sum()), kv_rows_touched=S, attn_desc=descx, ret_desc=rdesc0)
     else:
         scen = dict(prefill=True, entries=1, visible_keys=int((pos - (pos // chunk) * chunk + 1).sum()), kv_rows_touched=S, attn_desc=desc0)
     out["prefill"]["kernels"] = kernel_table(model, eng, prefill_once, scen, pk)

@@ -50,7 +50,7 @@ def rnd(*shape, seed=0, scale=1.0):
 
 
 # ---- token shift and post-norm ------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("W", [44, 33, 1024])
+@pytest.mark.parametrize("W", [44, 33, 1024, 4100])
 def test_token_shift_and_gated_post_norm_over_portions(ops, W):
     """two sequences in portions (one of them of two tokens, one a single token) that share the step; slots hold another sequence's
     leftovers at the start; the state is written by the post-norm of the mixer's sublayer, read by the shift of the next portion"""
