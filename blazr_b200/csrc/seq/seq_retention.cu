@@ -214,12 +214,19 @@ __global__ void retention_combine_kernel(const RetArgs a, const b200seq_step st)
     const float full = exp2f((float)RET_C * l2);
     float* slot = a.state + (int64_t)st.ent_slot[e] * per + idx;
     float S = st.ent_pos0[e] == 0 ? 0.f : *slot;
-    for (int c = 0; c < nc; ++c) {
-        float* p = a.seg_state + (int64_t)(c0 + c) * per + idx;
-        const float U = *p;
-        *p = S;
-        const int len = min(RET_C, n - c * RET_C);
-        S = fmaf(len == RET_C ? full : exp2f((float)len * l2), S, U);
+    constexpr int AHEAD = 8;   // the chunks' local states do not depend on the walk: fetch a batch of them before the dependent chain uses them
+    for (int c0b = 0; c0b < nc; c0b += AHEAD) {
+        float U[AHEAD];
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) U[j] = c0b + j < nc ? a.seg_state[(int64_t)(c0 + c0b + j) * per + idx] : 0.f;
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) {
+            const int c = c0b + j;
+            if (c >= nc) break;
+            a.seg_state[(int64_t)(c0 + c) * per + idx] = S;
+            const int len = min(RET_C, n - c * RET_C);
+            S = fmaf(len == RET_C ? full : exp2f((float)len * l2), S, U[j]);
+        }
     }
     *slot = S;
 }
