@@ -646,7 +646,7 @@ int b200seq_attn_ex(const float* qkvg, int64_t ld, const b200seq_step* st, const
                     const float* kpooled, const float* vpooled, void* out, int out_dtype, float* scratch, size_t scratch_floats, void* stream) {
     if (!qkvg || !st || !kpool || !out || !d || (!vpool && !d->latent_v)) return fail(B200SEQ_ERR_INVALID_ARG, "attn: bad arguments");
     if (int rc = desc_check(d, "attn")) return rc;
-    if (d->V > 256) return fail(B200SEQ_ERR_INVALID_ARG, "attn: value size <= 256");
+    if (d->V > 512) return fail(B200SEQ_ERR_INVALID_ARG, "attn: value size <= 512");
     if (d->pool > 0 && (!kpooled || !vpooled)) return fail(B200SEQ_ERR_INVALID_ARG, "attn: pooled blocks need their pools");
     if (st->T == 0) return 0;
     const int H = d->H, G = d->G, D = d->D, V = d->V, gated = d->gate_col >= 0;
@@ -658,7 +658,8 @@ int b200seq_attn_ex(const float* qkvg, int64_t ld, const b200seq_step* st, const
                gated, out, out_dtype, scratch, error_flag_dev(), d->sink, d->gate ? d->gate : qkvg + (gated ? d->gate_col : 0), d->gate ? d->gate_ld : ld, d->kv_ld > 0 ? d->kv_ld : (int64_t)G * D,
                d->kv_ld > 0 ? d->kv_ld : (d->latent_v ? (int64_t)G * D : (int64_t)G * V), d->ctx_rows, (d->kd > 0 && d->kd < D) ? d->kd : D, d->krot, d->krot_ld};
     if (d->latent_v) a.vpool = kpool;
-    const int VPT = V <= 64 ? 4 : (V <= 128 ? 8 : 16);
+    const int VPT = V <= 64 ? 4 : (V <= 128 ? 8 : (V <= 256 ? 16 : 32));
+    if (VPT == 32 && p.RT != 1) return fail(B200SEQ_ERR_UNSUPPORTED, "attn: value sizes above 256 only in steps of few tokens (one query row per thread)");
     const int RQ = 16 * p.RT, QS = ((D + 3) & ~3) + 4;
     size_t smem = ((size_t)(RQ + AT_KT) * QS + (size_t)AT_KT * 16 * VPT + (size_t)RQ * (AT_KT + 4)) * sizeof(float);
     if (smem > 72 * 1024) {   // fewer than three blocks per SM would fit: let V reuse the K tile
@@ -686,7 +687,8 @@ int b200seq_attn_ex(const float* qkvg, int64_t ld, const b200seq_step* st, const
     } else {
         if (VPT == 4) ATT_LAUNCH(1, 4);
         else if (VPT == 8) ATT_LAUNCH(1, 8);
-        else ATT_LAUNCH(1, 16);
+        else if (VPT == 16) ATT_LAUNCH(1, 16);
+        else ATT_LAUNCH(1, 32);
     }
 #undef ATT_LAUNCH
     if (e != cudaSuccess) return cuda_status(e, "attn attribute");

@@ -330,6 +330,18 @@ def test_latent_attention_finds_a_far_key_and_counts_the_sink_once(ops):
             close(got["a"][:580], ref[:580], 3e-5)
 
 
+def test_latent_attention_with_a_wide_latent(ops):
+    """a latent wider than 256: single tokens stay in the latent space (one query row per thread, 32 value columns each), portions attend over per-head keys"""
+    H, Dn, Rd, V, R, eps, scale, rot = 3, 16, 8, 24, 320, 1e-5, 0.2, {"dims": 8, "base": 1000.0}
+    kv, q, gate = rnd(60, R + Rd, seed=87), rnd(60, H * (Dn + Rd), seed=88), rnd(60, H, seed=89)
+    uk, uv = rnd(H * Dn, R, seed=83, scale=R ** -0.5).bfloat16().float(), rnd(H * V, R, seed=84, scale=R ** -0.5).bfloat16().float()
+    norm_w, sink = 1 + rnd(R, seed=85, scale=0.1), rnd(H, seed=86).to(DEV)
+    ref = latent_reference(kv, q, uk, uv, norm_w, sink.cpu(), gate, H, Dn, Rd, V, R, scale, eps, rot)
+    got = run_latent(ops, {"a": kv}, {"a": q}, {"a": gate}, uk, uv, norm_w, sink, H, Dn, Rd, V, R, scale, eps, rot, [[("a", 40)], [("a", 1)], [("a", 1)], [("a", 9)]] + [[("a", 1)]] * 9,
+                     {"a": pages_for(60)}, torch.zeros(4, 16, R + Rd, device=DEV), expanded=True)
+    close(got["a"], ref, 2e-5)
+
+
 def test_bfloat16_activations_in_latent_attention(ops):
     H, Dn, Rd, V, R, eps, scale, rot = 4, 16, 8, 16, 32, 1e-5, 0.2, {"dims": 8, "base": 100.0}
     kv, q, gate = rnd(80, R + Rd, seed=80), rnd(80, H * (Dn + Rd), seed=81), rnd(80, H, seed=82)
