@@ -127,9 +127,10 @@ class DenseFfSpec:
 
 @dataclass
 class MoeFfSpec:
-    """`top` of `experts` small feed-forwards (down(act(up h)), no gate branch) per token, chosen by sigmoid router scores among the experts
-    of the `keep` best of `groups` groups of neighbours, weighted by their scores normalised over the chosen; optionally a shared expert
-    of the same form for every token, times a sigmoid token gate"""
+    """`top` of `experts` small feed-forwards per token - down(act(up h)), or with a gate branch down(act(gate h, up h)) - plus optionally a
+    shared expert of the same form for every token.  router "sigmoid": the choice falls by sigmoid router scores among the experts of the
+    `keep` best of `groups` groups of neighbours, weighted by their scores normalised over the chosen, the shared expert times a sigmoid
+    token gate.  router "table": a table indexed by the token id names the experts, each weighted 1 / top, the shared expert is added as it is."""
     experts: int
     top: int
     ff: int

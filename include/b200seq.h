@@ -2,7 +2,10 @@
  * b200seq.h -- C ABI of libb200seq.so: dense (bfloat16-weight) linear layers and the sequence operators of
  * layer-list models on B200 (sm_100a): multi-stream residual mixing with grouped RMS norm, short causal
  * convolutions with carried state, chunk/window-masked attention over a paged KV pool, the selective
- * state-space recurrence with per-slot state, gated feed-forward activations, arg-max sampling.
+ * state-space recurrence with per-slot state, gated feed-forward activations, the depth-averaged residual,
+ * mixtures of experts (routed or chosen by a table), retention (fixed-decay linear attention), latent
+ * attention (low-rank key / value cache, soft-max sink), per-head projections, token shift and the gated
+ * post-norm residual, arg-max sampling.
  *
  * It sits beside libb200q (include/b200q.h), which holds the quantized linear layer; the conventions are
  * the same:
