@@ -82,6 +82,7 @@ class StepEntry:
     slot: int                   # recurrent-state slot of the request
     block_table: Sequence[int]  # KV pages of the request (must cover pos0 + len(tokens) positions)
     want: Sequence[int] = ()    # indices into `tokens` whose logits are wanted
+    prev: int = -1              # the request's last token before this portion (-1: none yet); models with a bigram embedding read it
 
 
 @dataclass
@@ -97,6 +98,7 @@ class StepArrays:
     want_rows: np.ndarray      # token rows whose logits are wanted, in entry order
     T: int
     B: int
+    ent_prev: Optional[np.ndarray] = None   # the token before each entry's first one (carried per request; unused at position 0)
 
     @property
     def decode_only(self) -> bool:
@@ -131,4 +133,5 @@ def build_step(entries: Sequence[StepEntry], block_size: int, max_blocks: Option
         tok_ent=np.repeat(np.arange(B, dtype=np.int32), lens),
         tok_pos=np.concatenate([np.arange(e.pos0, e.pos0 + n, dtype=np.int32) for e, n in zip(entries, lens)]) if B else np.zeros(0, np.int32),
         ent_start=start, ent_slot=np.asarray([e.slot for e in entries], dtype=np.int32),
-        ent_pos0=np.asarray([e.pos0 for e in entries], dtype=np.int32), block_table=bt, want_rows=np.asarray(want, dtype=np.int32), T=T, B=B)
+        ent_pos0=np.asarray([e.pos0 for e in entries], dtype=np.int32), block_table=bt, want_rows=np.asarray(want, dtype=np.int32), T=T, B=B,
+        ent_prev=np.asarray([max(int(e.prev), 0) for e in entries], dtype=np.int32))

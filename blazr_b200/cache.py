@@ -2,7 +2,8 @@
 
 The reference keeps a block allocator + per-sequence block tables for paged attention (src/engine/batch_engine.rs, block_size 16,
 src/config/inference.rs:94-98).  Layer-list models with recurrent layers need a second resource: one state slot per live request
-(convolution tails, state-space matrices), handed out on admission and returned on release.  Pages and slots are reused; a new
+(convolution tails, state-space matrices, element-wise recurrent states), handed out on admission and returned on release; the
+request's last token is kept beside it for embeddings that hash neighbouring tokens.  Pages and slots are reused; a new
 request never sees what the previous owner left because a sequence at position 0 reads its carried state as zero and its pages
 are written before they are read.
 """
@@ -66,6 +67,7 @@ class SeqState:
     slot: int
     blocks: List[int] = field(default_factory=list)
     n_tokens: int = 0          # tokens already in the cache / folded into the state
+    last_token: int = -1       # the last token fed (state of embeddings that hash the previous token with the current one)
 
 
 class CacheManager:

@@ -136,6 +136,90 @@ __global__ void attn_prep_kernel(float* __restrict__ proj, int64_t ld, b200seq_s
     }
 }
 
+// General form of the prep step, for layers that use what the kernel above leaves out: a bias of the projection row, an RMS norm WITH weights
+// (per head, weight [D] shared by the heads, or over the whole q / k projection at once, weights [H * D] / [G * D]), rotation of halves
+// (pairs (i, i + rot_dims / 2)), fewer value heads than key heads, keys and values that belong to another layer (only q is prepared).
+// grid (T), 256 threads, a warp per head unit; the unit's normalised values are staged in the warp's slice of shared memory so that the
+// rotation can read any partner.  Dynamic shared memory: rot_dims floats (cos, sin per pair) + 8 * Dmax (Dmax = max(D, V)) + 40.
+__global__ void attn_prep_gen_kernel(float* __restrict__ proj, int64_t ld, b200seq_step st, const b200seq_attn_desc a, float* __restrict__ kpool,
+                                     float* __restrict__ vpool, int Dmax, int* err) {
+    extern __shared__ float gsm[];
+    float* rot_sm = gsm;                       // [rot_dims / 2] cos | [rot_dims / 2] sin
+    float* stage = gsm + a.rot_dims;           // [8][Dmax]
+    float* red = stage + 8 * Dmax;
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int e = st.tok_ent[t], pos = st.tok_pos[t];
+    const int H = a.H, G = a.G, D = a.D, V = a.V;
+    const int Gv = a.vg > 0 ? a.vg : G;
+    const int np = a.rot_dims >> 1;
+    const int64_t row = a.kv_shared ? -1 : kv_row(st, e, pos, err);
+    float* base = proj + (int64_t)t * ld;
+    for (int i = threadIdx.x; i < np; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * a.rot_freq[i], &sn, &cs);
+        rot_sm[i] = cs * a.rot_scale, rot_sm[np + i] = sn * a.rot_scale;
+    }
+    float rq = 1.f, rk = 1.f;
+    if (a.norm_full && a.qk_eps >= 0.f) {   // one RMS over all heads of q, one over all heads of k
+        float sq = 0.f, sk = 0.f;
+        for (int i = threadIdx.x; i < H * D; i += blockDim.x) {
+            const float v = base[a.q_col + i] + (a.in_bias ? a.in_bias[a.q_col + i] : 0.f);
+            sq = fmaf(v, v, sq);
+        }
+        rq = 1.0f / sqrtf(block_sum(sq, red) / (float)(H * D) + a.qk_eps);
+        if (!a.kv_shared) {
+            for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+                const float v = base[a.k_col + i] + (a.in_bias ? a.in_bias[a.k_col + i] : 0.f);
+                sk = fmaf(v, v, sk);
+            }
+            rk = 1.0f / sqrtf(block_sum(sk, red) / (float)(G * D) + a.qk_eps);
+        }
+    }
+    __syncthreads();   // rot_sm
+    float* hs = stage + wid * Dmax;
+    const int nu = a.kv_shared ? H : H + G + Gv;
+    for (int u = wid; u < nu; u += nw) {
+        if (u < H + G) {
+            const bool isq = u < H;
+            const int hh = isq ? u : u - H;
+            const int col = (isq ? a.q_col : a.k_col) + hh * D;
+            const float* nw_ = isq ? a.q_norm_w : a.k_norm_w;
+            float ss = 0.f;
+            for (int d = lane; d < D; d += 32) {
+                const float v = base[col + d] + (a.in_bias ? a.in_bias[col + d] : 0.f);
+                hs[d] = v;
+                ss = fmaf(v, v, ss);
+            }
+            float rinv = 1.f;
+            if (a.qk_eps >= 0.f) rinv = a.norm_full ? (isq ? rq : rk) : 1.0f / sqrtf(warp_sum(ss) / (float)D + a.qk_eps);
+            for (int d = lane; d < D; d += 32) hs[d] = hs[d] * rinv * (nw_ ? nw_[a.norm_full ? hh * D + d : d] : 1.f);
+            __syncwarp();
+            float* dst = isq ? base + col : (row >= 0 ? kpool + (row * G + hh) * D : nullptr);
+            if (dst) {
+                for (int d = lane; d < D; d += 32) {
+                    float v = hs[d];
+                    if (d < a.rot_dims) {
+                        int i, pd;
+                        bool first;
+                        if (a.rot_half) first = d < np, i = first ? d : d - np, pd = first ? d + np : d - np;
+                        else first = !(d & 1), i = d >> 1, pd = d ^ 1;
+                        const float cs = rot_sm[i], sn = rot_sm[np + i], o = hs[pd];
+                        v = first ? fmaf(v, cs, -o * sn) : fmaf(v, cs, o * sn);
+                    }
+                    dst[d] = v;
+                }
+            }
+            __syncwarp();   // hs is reused by the warp's next unit
+        } else if (row >= 0) {
+            const int g = u - H - G;
+            const int col = a.v_col + g * V;
+            float* dst = vpool + (row * Gv + g) * V;
+            for (int d = lane; d < V; d += 32) dst[d] = base[col + d] + (a.in_bias ? a.in_bias[col + d] : 0.f);
+        }
+    }
+}
+
 // grid (T, column slices): the token that completes a block of P positions writes the block's mean key and mean value, one column per thread
 __global__ void attn_pool_kernel(b200seq_step st, int G, int D, int V, int P, int ppp, const float* __restrict__ kpool, const float* __restrict__ vpool,
                                  float* __restrict__ kpp, float* __restrict__ vpp, int* err) {
@@ -280,6 +364,11 @@ struct AttnArgs {
     int kd;              // floats of a key head that lie in kpool (at g * kd); the remaining D - kd come from krot, one part for all heads
     const float* krot;   // paged rows of krld floats (pointer already at the part's first column), or null
     int64_t krld;
+    const float* head_scale;   // [H] or null: one more factor of head h's scores
+    float softcap;             // > 0: score <- softcap * tanh(score / softcap)
+    int keep_first;            // with a window: positions below this stay visible to all later positions
+    int vdiv;                  // key head g reads value head g / vdiv
+    int gate_elem;             // the gate has one logit per output element: gate[t * gld + h * V + c]
 };
 
 __device__ __forceinline__ bool attn_find_tile(const b200seq_step& st, int idx, int QT, int& e, int& t0, int& nq) {
@@ -341,7 +430,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
     }
     // per-row limits of the visible keys
     int rlo[RT], rhi[RT], rnb[RT];   // visible positions [rlo, rhi]; visible pooled blocks [0, rnb)
-    float m[RT], l[RT], acc[RT][VPT];
+    float m[RT], l[RT], acc[RT][VPT], rsc[RT];
 #pragma unroll
     for (int i = 0; i < RT; ++i) {
         const int r = ty * RT + i;
@@ -352,8 +441,10 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
             if (a.window > 0) lo = max(lo, p - a.window + 1);
             rlo[i] = lo, rhi[i] = p;
             rnb[i] = (a.pool > 0 && p - a.window + 1 > 0) ? (p - a.window + 1) / a.pool : 0;
+            rsc[i] = a.head_scale ? a.scale * a.head_scale[h0 + hr] : a.scale;
         } else {
             rlo[i] = 1, rhi[i] = 0, rnb[i] = 0;   // sees nothing
+            rsc[i] = a.scale;
         }
         m[i] = -INFINITY, l[i] = 0.f;
 #pragma unroll
@@ -363,14 +454,19 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
     // pooled blocks every row of the tile may see (the tile's last row sees the most), then the positions from kbeg to hi
     const int nbmax = (a.pool > 0 && hi - a.window + 1 > 0) ? (hi - a.window + 1) / a.pool : 0;
     const int npt = (nbmax + AT_KT - 1) / AT_KT;
-    const int ntiles = npt + (hi - kbeg) / AT_KT + 1;
-    auto load_v = [&](int k0, bool pooled) {
+    // kept first positions that lie before the window of the tile's first row: tiles of their own, seen by every row of the tile; those
+    // inside [kbeg, hi] come with the window tiles (a later row's window may have left them behind: the row test below keeps them)
+    const int keep = (a.window > 0 && a.keep_first > 0) ? a.keep_first : 0;
+    const int nfirst = min(keep, kbeg);
+    const int nft = (nfirst + AT_KT - 1) / AT_KT;
+    const int ntiles = npt + nft + (hi - kbeg) / AT_KT + 1;
+    auto load_v = [&](int k0, bool pooled, int klim) {
         const int k = tid >> 2, sub = tid & 3;
         const int kp = k0 + k;
-        const bool in = pooled ? kp < nbmax : kp <= hi;
+        const bool in = pooled ? kp < nbmax : kp <= klim;
         const float* src = !in ? nullptr
                            : pooled ? a.vpp + (pooled_row(bt, bs, a.pool, a.ppp, kp) * G + g) * V
-                                    : a.vpool + (a.ctx_rows ? cstart + kp : (int64_t)bt[kp / bs] * bs + kp % bs) * a.vld + (int64_t)g * V;
+                                    : a.vpool + (a.ctx_rows ? cstart + kp : (int64_t)bt[kp / bs] * bs + kp % bs) * a.vld + (int64_t)(g / a.vdiv) * V;
         if (vecV) {
             for (int c4 = sub; c4 < (VS >> 2); c4 += 4)
                 *reinterpret_cast<float4*>(Vs + k * VS + 4 * c4) = (in && 4 * c4 < V) ? *reinterpret_cast<const float4*>(src + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -381,12 +477,14 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
     for (int tile = 0; tile < ntiles; ++tile) {
         if (tile % a.nsplit != split) continue;
         const bool pooled = tile < npt;
-        const int k0 = pooled ? tile * AT_KT : kbeg + (tile - npt) * AT_KT;
+        const bool first = !pooled && tile < npt + nft;
+        const int k0 = pooled ? tile * AT_KT : (first ? (tile - npt) * AT_KT : kbeg + (tile - npt - nft) * AT_KT);
+        const int klim = first ? nfirst - 1 : hi;   // last position this tile may load
         __syncthreads();   // the previous tile's products are done with Ks, Vs, Ps (and Qs is written before the first)
         {   // four threads per key: the page lookup happens once per thread and tile
             const int k = tid >> 2, sub = tid & 3;
             const int kp = k0 + k;
-            const bool in = pooled ? kp < nbmax : kp <= hi;
+            const bool in = pooled ? kp < nbmax : kp <= klim;
             const int64_t prow = (in && !pooled) ? (int64_t)bt[kp / bs] * bs + kp % bs : 0;
             const float* src = !in ? nullptr
                                : pooled ? a.kpp + (pooled_row(bt, bs, a.pool, a.ppp, kp) * G + g) * D
@@ -400,7 +498,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
                 for (int d = sub; d < Dp; d += 4) Ks[k * QS + d] = (in && d < D) ? (d < kd ? src[d] : src2[d]) : 0.f;
             }
         }
-        if (!a.share_kv) load_v(k0, pooled);
+        if (!a.share_kv) load_v(k0, pooled, klim);
         __syncthreads();
         float s[RT][4];
 #pragma unroll
@@ -424,8 +522,10 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int kp = k0 + tx + 16 * j;
-                const bool seen = pooled ? kp < rnb[i] : (kp >= rlo[i] && kp <= rhi[i]);
-                s[i][j] = seen ? s[i][j] * a.scale : -INFINITY;
+                const bool seen = pooled ? kp < rnb[i] : (first ? (kp < nfirst && rhi[i] >= rlo[i]) : ((kp >= rlo[i] || kp < keep) && kp <= rhi[i]));
+                float sv = s[i][j] * rsc[i];
+                if (a.softcap > 0.f) sv = a.softcap * tanhf(sv / a.softcap);
+                s[i][j] = seen ? sv : -INFINITY;
                 mx = fmaxf(mx, s[i][j]);
             }
 #pragma unroll
@@ -454,7 +554,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
         }
         __syncthreads();
         if (a.share_kv) {   // every thread is done with the K tile: the V tile takes its place
-            load_v(k0, pooled);
+            load_v(k0, pooled, klim);
             __syncthreads();
         }
         for (int k = 0; k < AT_KT; k += 4) {
@@ -486,7 +586,7 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
         const int t = t0 + tq, h = h0 + hr;
         if (a.nsplit == 1) {
             float gate = 1.f;
-            if (a.gated) gate = sigmoidf_acc(a.gate[(int64_t)t * a.gld + h]);
+            if (a.gated && !a.gate_elem) gate = sigmoidf_acc(a.gate[(int64_t)t * a.gld + h]);
             float den = l[i], resc = 1.f;
             if (a.sink) {   // the sink's term, under the larger of the two maxima
                 const float sk = a.sink[h], mn = fmaxf(m[i], sk);
@@ -499,7 +599,10 @@ __global__ void __launch_bounds__(AT_NT, (VPT == 4) ? 3 : (VPT == 8 ? 2 : 1)) at
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int c = jv * 64 + tx * 4 + u;
-                    if (c < V) store_act(a.out, a.out_dtype, ((int64_t)t * H + h) * V + c, acc[i][4 * jv + u] * f);
+                    if (c < V) {
+                        const float ge = a.gate_elem ? sigmoidf_acc(a.gate[(int64_t)t * a.gld + (int64_t)h * V + c]) : 1.f;
+                        store_act(a.out, a.out_dtype, ((int64_t)t * H + h) * V + c, acc[i][4 * jv + u] * f * ge);
+                    }
                 }
         } else {
             float* pp = a.part + (((int64_t)t * H + h) * a.nsplit + split) * (V + 2);
@@ -528,8 +631,9 @@ __global__ void attn_merge_kernel(const AttnArgs a) {
         if (ms != -INFINITY) L = fmaf(pp[s * (V + 2) + 1], expf(ms - M), L);
     }
     float gate = 1.f;
-    if (a.gated) gate = sigmoidf_acc(a.gate[(int64_t)t * a.gld + h]);
+    if (a.gated && !a.gate_elem) gate = sigmoidf_acc(a.gate[(int64_t)t * a.gld + h]);
     for (int c = threadIdx.x; c < V; c += blockDim.x) {
+        if (a.gate_elem) gate = sigmoidf_acc(a.gate[(int64_t)t * a.gld + (int64_t)h * V + c]);
         float o = 0.f;
         for (int s = 0; s < ns; ++s) {
             const float ms = pp[s * (V + 2)];
@@ -576,6 +680,12 @@ static int desc_check(const b200seq_attn_desc* d, const char* what) {
     if (d->rot_dims < 0 || d->rot_dims > d->D || (d->rot_dims & 1) || (d->rot_dims > 0 && !d->rot_freq))
         return fail(B200SEQ_ERR_INVALID_ARG, "%s: rotary dimensions must be even, at most D, with a frequency table", what);
     if (d->pool < 0 || (d->pool > 0 && d->window < 1)) return fail(B200SEQ_ERR_INVALID_ARG, "%s: pooled blocks need a window", what);
+    if (d->vg < 0 || (d->vg > 0 && (d->G % d->vg || d->pool > 0 || d->latent_v || d->v_col == d->k_col)))
+        return fail(B200SEQ_ERR_INVALID_ARG, "%s: the value heads must divide the key heads (no pooled blocks, own value columns)", what);
+    if (d->keep_first < 0 || (d->keep_first > 0 && (d->window < 1 || d->chunk > 0 || d->pool > 0)))
+        return fail(B200SEQ_ERR_INVALID_ARG, "%s: kept first positions go with a window (no chunks, no pooled blocks)", what);
+    if ((d->q_norm_w || d->k_norm_w || d->norm_full) && d->qk_eps < 0.f) return fail(B200SEQ_ERR_INVALID_ARG, "%s: norm weights need qk_eps >= 0", what);
+    if (d->kv_shared && (d->pool > 0 || d->v_col == d->k_col)) return fail(B200SEQ_ERR_INVALID_ARG, "%s: shared keys / values go with plain pools", what);
     return 0;
 }
 
@@ -583,10 +693,19 @@ extern "C" {
 
 int b200seq_attn_prep_ex(float* proj, int64_t ld, const b200seq_step* st, const b200seq_attn_desc* d, float* kpool, float* vpool, float* kpooled, float* vpooled,
                          void* stream) {
-    if (!proj || !st || !kpool || !vpool) return fail(B200SEQ_ERR_INVALID_ARG, "attn_prep: bad arguments");
+    if (!proj || !st || !d || ((!kpool || !vpool) && !d->kv_shared)) return fail(B200SEQ_ERR_INVALID_ARG, "attn_prep: bad arguments");
     if (int rc = desc_check(d, "attn_prep")) return rc;
     if (d->pool > 0 && (!kpooled || !vpooled)) return fail(B200SEQ_ERR_INVALID_ARG, "attn_prep: pooled blocks need their pools");
     if (st->T == 0) return 0;
+    if (d->q_norm_w || d->k_norm_w || d->norm_full || d->rot_half || d->in_bias || d->kv_shared || d->vg > 0) {
+        if (d->pool > 0 || d->v_col == d->k_col) return fail(B200SEQ_ERR_UNSUPPORTED, "attn_prep: the general form has no pooled blocks and own value columns");
+        const int Dmax = d->D > d->V ? d->D : d->V;
+        const size_t smem = (size_t)(d->rot_dims + 8 * Dmax + 40) * sizeof(float);
+        if (smem > 48 * 1024) return fail(B200SEQ_ERR_UNSUPPORTED, "attn_prep: head size too large");
+        attn_prep_gen_kernel<<<st->T, 256, smem, (cudaStream_t)stream>>>(proj, ld, *st, *d, kpool, vpool, Dmax, error_flag_dev());
+        SEQ_LAUNCH_CHECK("attn_prep");
+        return 0;
+    }
     const int fuse_pool = d->pool > 0 && st->T == st->B;   // one token per entry: no other block of this step writes a row the mean reads
     attn_prep_kernel<<<st->T, 256, (size_t)d->rot_dims * sizeof(float), (cudaStream_t)stream>>>(proj, ld, *st, *d, kpool, vpool, kpooled, vpooled, fuse_pool,
                                                                                                  error_flag_dev());
@@ -628,12 +747,13 @@ int b200seq_latent_gather(const float* kpool, int64_t kld, const b200seq_step* s
     return 0;
 }
 
-static int attn_max_keys(const b200seq_step* st, int chunk, int window, int pool) {
+static int attn_max_keys(const b200seq_step* st, int chunk, int window, int pool, int keep_first = 0) {
     const int ctx = st->max_blocks * st->block_size;
     int max_keys = ctx;
     if (chunk > 0 && chunk < max_keys) max_keys = chunk;
     if (window > 0 && window < max_keys) max_keys = window;
     if (pool > 0) max_keys += ctx / pool;
+    if (window > 0 && keep_first > 0) max_keys = max_keys + keep_first < ctx ? max_keys + keep_first : ctx;
     return max_keys;
 }
 size_t b200seq_attn_scratch_floats(int T, int B, int H, int G, int V, int max_keys) {
@@ -650,13 +770,14 @@ int b200seq_attn_ex(const float* qkvg, int64_t ld, const b200seq_step* st, const
     if (d->pool > 0 && (!kpooled || !vpooled)) return fail(B200SEQ_ERR_INVALID_ARG, "attn: pooled blocks need their pools");
     if (st->T == 0) return 0;
     const int H = d->H, G = d->G, D = d->D, V = d->V, gated = d->gate_col >= 0;
-    const int max_keys = attn_max_keys(st, d->chunk, d->window, d->pool);
+    const int max_keys = attn_max_keys(st, d->chunk, d->window, d->pool, d->keep_first);
     AttnPlan p = attn_plan(st->T, st->B, H, G, max_keys);
     if (p.nsplit > 1 && (!scratch || scratch_floats < (size_t)st->T * H * p.nsplit * (V + 2))) p.nsplit = 1;
     const int ppp = d->pool > 0 ? (st->block_size + d->pool - 1) / d->pool : 0;
     AttnArgs a{qkvg, ld, kpool, vpool, kpooled, vpooled, d->pool, ppp, d->q_col, d->gate_col, H, G, D, V, p.Rb, p.HB, p.QT, p.nsplit, 0, d->scale, d->chunk, d->window,
                gated, out, out_dtype, scratch, error_flag_dev(), d->sink, d->gate ? d->gate : qkvg + (gated ? d->gate_col : 0), d->gate ? d->gate_ld : ld, d->kv_ld > 0 ? d->kv_ld : (int64_t)G * D,
-               d->kv_ld > 0 ? d->kv_ld : (d->latent_v ? (int64_t)G * D : (int64_t)G * V), d->ctx_rows, (d->kd > 0 && d->kd < D) ? d->kd : D, d->krot, d->krot_ld};
+               d->kv_ld > 0 ? d->kv_ld : (d->latent_v ? (int64_t)G * D : (int64_t)(d->vg > 0 ? d->vg : G) * V), d->ctx_rows, (d->kd > 0 && d->kd < D) ? d->kd : D, d->krot, d->krot_ld,
+               d->head_scale, d->softcap, d->keep_first, d->vg > 0 ? G / d->vg : 1, (gated && d->gate_elem) ? 1 : 0};
     if (d->latent_v) a.vpool = kpool;
     const int VPT = V <= 64 ? 4 : (V <= 128 ? 8 : (V <= 256 ? 16 : 32));
     if (VPT == 32 && p.RT != 1) return fail(B200SEQ_ERR_UNSUPPORTED, "attn: value sizes above 256 only in steps of few tokens (one query row per thread)");

@@ -192,17 +192,18 @@ __global__ void hc_norm_kernel(float* __restrict__ X, const float* __restrict__ 
 // token, so no other thread touches that state.
 constexpr int CONV_TILE = 16;
 template <int VW>
-__global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ w, const float* __restrict__ bias,
-                                   float* __restrict__ state, b200seq_step st, int C, int taps, int mode, void* __restrict__ out, int out_dtype,
-                                   int64_t ldo) {
+__global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ in_bias, const float* __restrict__ w,
+                                   const float* __restrict__ bias, float* __restrict__ state, b200seq_step st, int C, int taps, int mode,
+                                   void* __restrict__ out, int out_dtype, int64_t ldo, void* __restrict__ out2, int out2_dtype, int64_t ldo2) {
     const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * VW;
     if (c0 >= C) return;
-    float wr[VW][MAX_TAPS], b[VW];
+    float wr[VW][MAX_TAPS], b[VW], ib[VW];   // ib: bias of the input (the convolution sees x + ib; the carried state holds biased inputs)
 #pragma unroll
     for (int e = 0; e < VW; ++e) {
 #pragma unroll
         for (int j = 0; j < MAX_TAPS; ++j) wr[e][j] = j < taps ? w[(int64_t)(c0 + e) * taps + j] : 0.f;
         b[e] = bias ? bias[c0 + e] : 0.f;
+        ib[e] = in_bias ? in_bias[c0 + e] : 0.f;
     }
     const int hist = taps - 1;
     auto finish = [&](float acc, float bb, float xin) {
@@ -230,7 +231,7 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, con
                 for (int j = 0; j < MAX_TAPS; ++j) old[j] = (j < hist && !fresh) ? state[sbase + (int64_t)j * C] : 0.f;
                 // input at entry-relative index idx (negative = carried)
                 auto src = [&](int idx) -> float {
-                    if (idx >= 0) return x[(int64_t)(s0 + idx) * ldx + c];
+                    if (idx >= 0) return x[(int64_t)(s0 + idx) * ldx + c] + ib[e];
                     float v = 0.f;
 #pragma unroll
                     for (int j = 0; j < MAX_TAPS; ++j)
@@ -242,7 +243,9 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, con
 #pragma unroll
                     for (int j = 0; j < MAX_TAPS; ++j)
                         if (j < taps) acc = fmaf(wr[e][j], src(ii - hist + j), acc);
-                    store_act(out, out_dtype, (int64_t)(s0 + ii) * ldo + c, finish(acc, b[e], x[(int64_t)(s0 + ii) * ldx + c]));
+                    const float r = finish(acc, b[e], x[(int64_t)(s0 + ii) * ldx + c] + ib[e]);
+                    store_act(out, out_dtype, (int64_t)(s0 + ii) * ldo + c, r);
+                    if (out2) store_act(out2, out2_dtype, (int64_t)(s0 + ii) * ldo2 + c, r);
                 }
                 float nv[MAX_TAPS];
 #pragma unroll
@@ -262,9 +265,9 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, con
                 const float* xp = x + (int64_t)(t - hist + j) * ldx + c0;
                 if (VW == 4) {
                     const float4 v = *reinterpret_cast<const float4*>(xp);
-                    cur[0] = v.x, cur[1 % VW] = v.y, cur[2 % VW] = v.z, cur[3 % VW] = v.w;
+                    cur[0] = v.x + ib[0], cur[1 % VW] = v.y + ib[1 % VW], cur[2 % VW] = v.z + ib[2 % VW], cur[3 % VW] = v.w + ib[3 % VW];
                 } else {
-                    cur[0] = xp[0];
+                    cur[0] = xp[0] + ib[0];
                 }
 #pragma unroll
                 for (int e = 0; e < VW; ++e) acc[e] = fmaf(wr[e][j], cur[e], acc[e]);
@@ -285,6 +288,10 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, con
             }
         } else {
             store_act(out, out_dtype, (int64_t)t * ldo + c0, v[0]);
+        }
+        if (out2) {
+#pragma unroll
+            for (int e = 0; e < VW; ++e) store_act(out2, out2_dtype, (int64_t)t * ldo2 + c0 + e, v[e]);
         }
     }
 }
@@ -450,16 +457,22 @@ static int hc_norm_launch(float* X, const float* y, const float* post, const flo
 
 int b200seq_causal_conv(const float* x, int64_t ldx, const float* w, const float* bias, float* state, const b200seq_step* st, int C, int taps, int mode,
                         void* out, int out_dtype, int64_t ldo, void* stream) {
+    return b200seq_causal_conv_ex(x, ldx, nullptr, w, bias, state, st, C, taps, mode, out, out_dtype, ldo, nullptr, B200SEQ_F32, 0, stream);
+}
+
+int b200seq_causal_conv_ex(const float* x, int64_t ldx, const float* in_bias, const float* w, const float* bias, float* state, const b200seq_step* st, int C, int taps,
+                           int mode, void* out, int out_dtype, int64_t ldo, void* out2, int out2_dtype, int64_t ldo2, void* stream) {
     if (!x || !w || !st || !out || C < 1 || taps < 1 || taps > MAX_TAPS || (taps > 1 && !state)) return fail(B200SEQ_ERR_INVALID_ARG, "causal_conv: bad arguments (1 <= taps <= %d)", MAX_TAPS);
     if (out_dtype != B200SEQ_F32 && out_dtype != B200SEQ_BF16) return fail(B200SEQ_ERR_INVALID_ARG, "causal_conv: output dtype");
+    if (out2 && ((out2_dtype != B200SEQ_F32 && out2_dtype != B200SEQ_BF16) || ldo2 < C)) return fail(B200SEQ_ERR_INVALID_ARG, "causal_conv: second output");
     if (st->T == 0) return 0;
     const bool vec = C % 4 == 0 && ldx % 4 == 0 && ldo % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     if (vec) {
         dim3 grid((C / 4 + 127) / 128, (st->T + CONV_TILE - 1) / CONV_TILE);
-        causal_conv_kernel<4><<<grid, 128, 0, (cudaStream_t)stream>>>(x, ldx, w, bias, state, *st, C, taps, mode, out, out_dtype, ldo);
+        causal_conv_kernel<4><<<grid, 128, 0, (cudaStream_t)stream>>>(x, ldx, in_bias, w, bias, state, *st, C, taps, mode, out, out_dtype, ldo, out2, out2_dtype, ldo2);
     } else {
         dim3 grid((C + 127) / 128, (st->T + CONV_TILE - 1) / CONV_TILE);
-        causal_conv_kernel<1><<<grid, 128, 0, (cudaStream_t)stream>>>(x, ldx, w, bias, state, *st, C, taps, mode, out, out_dtype, ldo);
+        causal_conv_kernel<1><<<grid, 128, 0, (cudaStream_t)stream>>>(x, ldx, in_bias, w, bias, state, *st, C, taps, mode, out, out_dtype, ldo, out2, out2_dtype, ldo2);
     }
     SEQ_LAUNCH_CHECK("causal_conv");
     return 0;

@@ -35,14 +35,32 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, int64_t l
 }
 
 // choice of one token by one warp: zr = its E router logits; sm = 2 * E + groups floats of shared memory
+// kind 0: sigmoid scores; kind 1: soft-max over the E logits.  corr (or null) is added to the scores for the choice only.
 __device__ __forceinline__ void route_token(const float* zr, float* sm, int t, int lane, int E, int groups, int keep, int top, int32_t* __restrict__ ids,
-                                            float* __restrict__ wts, int32_t* __restrict__ counts) {
-    float* s = sm;            // [E] scores; a chosen or excluded expert is marked by a negative value in `avail`
-    float* avail = sm + E;    // [E]
+                                            float* __restrict__ wts, int32_t* __restrict__ counts, int kind = 0, const float* __restrict__ corr = nullptr) {
+    float* s = sm;            // [E] scores
+    float* avail = sm + E;    // [E] choice scores; a chosen or excluded expert is marked by -inf
     float* gsc = avail + E;   // [groups]
-    for (int e = lane; e < E; e += 32) {
-        const float v = sigmoidf_acc(zr[e]);
-        s[e] = v, avail[e] = v;
+    if (kind == 1) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
+        mx = warp_max(mx);
+        float den = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float v = expf(zr[e] - mx);
+            s[e] = v;
+            den += v;
+        }
+        den = warp_sum(den);
+        for (int e = lane; e < E; e += 32) {
+            const float v = s[e] / den;
+            s[e] = v, avail[e] = v + (corr ? corr[e] : 0.f);
+        }
+    } else {
+        for (int e = lane; e < E; e += 32) {
+            const float v = sigmoidf_acc(zr[e]);
+            s[e] = v, avail[e] = v + (corr ? corr[e] : 0.f);
+        }
     }
     __syncwarp();
     if (groups > 1 && keep < groups) {
@@ -72,12 +90,12 @@ __device__ __forceinline__ void route_token(const float* zr, float* sm, int t, i
             __syncwarp();
         }
         for (int e = lane; e < E; e += 32)
-            if (gsc[e / gs] != -2.f) avail[e] = -1.f;
+            if (gsc[e / gs] != -2.f) avail[e] = -INFINITY;
         __syncwarp();
     }
     float sum = 0.f;
     for (int k = 0; k < top; ++k) {
-        float best = -1.f;
+        float best = -INFINITY;
         int arg = 0x7fffffff;
         for (int e = lane; e < E; e += 32)
             if (avail[e] > best) best = avail[e], arg = e;
@@ -86,11 +104,13 @@ __device__ __forceinline__ void route_token(const float* zr, float* sm, int t, i
             const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ov > best || (ov == best && oi < arg)) best = ov, arg = oi;
         }
-        if (arg == 0x7fffffff) arg = 0, best = 0.f;   // fewer allowed experts than `top`: cannot happen with a valid configuration
+        if (arg == 0x7fffffff) arg = 0;   // fewer allowed experts than `top`: cannot happen with a valid configuration
+        best = s[arg];                    // the weight is the score itself, without the correction
+        __syncwarp();
         if (lane == 0) {
             ids[(int64_t)t * top + k] = arg;
             wts[(int64_t)t * top + k] = best;
-            avail[arg] = -1.f;
+            avail[arg] = -INFINITY;
             if (counts) atomicAdd(&counts[arg], 1);
         }
         sum += best;
@@ -103,9 +123,9 @@ __device__ __forceinline__ void route_token(const float* zr, float* sm, int t, i
 
 // grid (T), one warp per token
 __global__ void moe_route_kernel(const float* __restrict__ z, int64_t ldz, int E, int groups, int keep, int top, int32_t* __restrict__ ids,
-                                 float* __restrict__ wts, int32_t* __restrict__ counts) {
+                                 float* __restrict__ wts, int32_t* __restrict__ counts, int kind, const float* __restrict__ corr) {
     extern __shared__ float sm[];
-    route_token(z + (int64_t)blockIdx.x * ldz, sm, blockIdx.x, threadIdx.x, E, groups, keep, top, ids, wts, counts);
+    route_token(z + (int64_t)blockIdx.x * ldz, sm, blockIdx.x, threadIdx.x, E, groups, keep, top, ids, wts, counts, kind, corr);
 }
 
 // choice by table: one thread per (token, choice)
@@ -274,6 +294,7 @@ __global__ void __launch_bounds__(256) moe_rows_gated_kernel(const MoeLin a) {
     const int p = blockIdx.y;
     if (2 * f + 1 >= a.N) return;
     const int e = a.ids[p];
+    if (e >= a.E) return;   // an expert without weights (identity): the pair has no row here
     const __nv_bfloat16* wr = a.w + ((int64_t)e * a.N + 2 * f) * a.K;
     const XT* xr = reinterpret_cast<const XT*>(a.x) + (int64_t)(a.x_div > 0 ? p / a.x_div : p) * a.ldx;
     const float g = warp_sum(moe_row_dot<XT, VEC>(wr, xr, a.K, lane));
@@ -289,6 +310,7 @@ __global__ void __launch_bounds__(256) moe_rows_kernel(const MoeLin a) {
     const int p = blockIdx.y;
     if (n >= a.N) return;
     const int e = a.ids[p];
+    if (e >= a.E) return;
     const __nv_bfloat16* wr = a.w + ((int64_t)e * a.N + n) * a.K;
     const XT* xr = reinterpret_cast<const XT*>(a.x) + (int64_t)(a.x_div > 0 ? p / a.x_div : p) * a.ldx;
     float acc = 0.f;
@@ -477,7 +499,8 @@ __global__ void __launch_bounds__(256) head_tiled_kernel(const HeadLin a) {
 
 // grid (T)
 __global__ void moe_combine_kernel(const float* __restrict__ ys, const float* __restrict__ wts, const int32_t* __restrict__ slot_of, int top, int W,
-                                   const float* __restrict__ shared, const float* __restrict__ gate_z, int64_t ldg, float* __restrict__ y) {
+                                   const float* __restrict__ shared, const float* __restrict__ gate_z, int64_t ldg, float* __restrict__ y,
+                                   const int32_t* __restrict__ ids, int E_real, const float* __restrict__ x_id) {
     const int64_t t = blockIdx.x;
     float gate = 1.f;
     if (shared && gate_z) gate = sigmoidf_acc(gate_z[t * ldg]);
@@ -486,7 +509,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ ys, const float* __
         for (int j = 0; j < top; ++j) {
             const int64_t p = t * top + j;
             const int64_t slot = slot_of ? slot_of[p] : p;
-            acc = fmaf(wts[p], ys[slot * W + c], acc);
+            acc = fmaf(wts[p], (ids && ids[p] >= E_real) ? x_id[t * W + c] : ys[slot * W + c], acc);
         }
         if (shared) acc = fmaf(gate, shared[t * W + c], acc);
         y[t * W + c] = acc;
@@ -500,6 +523,12 @@ using namespace b200seq;
 extern "C" {
 
 int b200seq_moe_route(const float* z, int64_t ldz, int T, int E, int groups, int keep, int top, int32_t* ids, float* wts, int32_t* counts, void* stream) {
+    return b200seq_moe_route_ex(z, ldz, T, E, groups, keep, top, 0, nullptr, ids, wts, counts, stream);
+}
+
+int b200seq_moe_route_ex(const float* z, int64_t ldz, int T, int E, int groups, int keep, int top, int kind, const float* correction, int32_t* ids, float* wts,
+                         int32_t* counts, void* stream) {
+    if (kind != 0 && kind != 1) return fail(B200SEQ_ERR_INVALID_ARG, "moe_route: score kind 0 (sigmoid) or 1 (soft-max)");
     if (!z || !ids || !wts || T < 0 || E < 1 || E > MOE_MAX_E || top < 1 || top > E || ldz < E) return fail(B200SEQ_ERR_INVALID_ARG, "moe_route: bad arguments (experts <= %d)", MOE_MAX_E);
     if (groups > 1 && (E % groups || keep < 1 || keep > groups || (int64_t)keep * (E / groups) < top))
         return fail(B200SEQ_ERR_INVALID_ARG, "moe_route: groups must divide the experts and the kept groups must hold `top` experts");
@@ -510,7 +539,7 @@ int b200seq_moe_route(const float* z, int64_t ldz, int T, int E, int groups, int
     }
     if (T == 0) return 0;
     const int g = groups > 1 ? groups : 1;
-    moe_route_kernel<<<T, 32, (size_t)(2 * E + g) * sizeof(float), cs>>>(z, ldz, E, g, groups > 1 ? keep : 1, top, ids, wts, counts);
+    moe_route_kernel<<<T, 32, (size_t)(2 * E + g) * sizeof(float), cs>>>(z, ldz, E, g, groups > 1 ? keep : 1, top, ids, wts, counts, kind, correction);
     SEQ_LAUNCH_CHECK("moe_route");
     return 0;
 }
@@ -665,9 +694,14 @@ int b200seq_moe_gather(const void* x_bf16, int64_t ldx_, const int32_t* sorted, 
 
 int b200seq_moe_combine(const float* ys, const float* wts, const int32_t* slot_of, int T, int top, int W, const float* shared, const float* gate_z, int64_t ldg,
                         float* y, void* stream) {
-    if (!ys || !wts || !y || T < 0 || top < 1 || W < 1) return fail(B200SEQ_ERR_INVALID_ARG, "moe_combine: bad arguments");
+    return b200seq_moe_combine_ex(ys, wts, slot_of, nullptr, 0, nullptr, T, top, W, shared, gate_z, ldg, y, stream);
+}
+
+int b200seq_moe_combine_ex(const float* ys, const float* wts, const int32_t* slot_of, const int32_t* ids, int E_real, const float* x_id, int T, int top, int W,
+                           const float* shared, const float* gate_z, int64_t ldg, float* y, void* stream) {
+    if (!ys || !wts || !y || T < 0 || top < 1 || W < 1 || (ids && !x_id)) return fail(B200SEQ_ERR_INVALID_ARG, "moe_combine: bad arguments");
     if (T == 0) return 0;
-    moe_combine_kernel<<<T, W >= 1024 ? 256 : 128, 0, (cudaStream_t)stream>>>(ys, wts, slot_of, top, W, shared, gate_z, ldg, y);
+    moe_combine_kernel<<<T, W >= 1024 ? 256 : 128, 0, (cudaStream_t)stream>>>(ys, wts, slot_of, top, W, shared, gate_z, ldg, y, ids, E_real, x_id);
     SEQ_LAUNCH_CHECK("moe_combine");
     return 0;
 }

@@ -73,11 +73,12 @@ class Engine:
             seen.add(rid)
             seq = self.cache.live.get(rid) or self.cache.admit(rid)
             self.cache.reserve(seq, len(toks))
-            entries.append(StepEntry(tokens=toks, pos0=seq.n_tokens, slot=seq.slot, block_table=seq.blocks, want=want))
+            entries.append(StepEntry(tokens=toks, pos0=seq.n_tokens, slot=seq.slot, block_table=seq.blocks, want=want, prev=seq.last_token))
         sa = build_step(entries, self.cache.block_size)
         logits = self.model.forward(sa, sample=sample)
         for rid, toks, _ in batch:
             self.cache.live[rid].n_tokens += len(toks)
+            self.cache.live[rid].last_token = int(toks[-1])
         self.steps += 1
         return logits
 

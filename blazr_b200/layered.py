@@ -7,7 +7,11 @@ wrapped in the pieces a design switches on.  Three layouts of the residual path 
              layer inputs are learned averages over the results of all earlier layers (blazr_b200/gemosun.py);
   "post":    sublayers in sequence that read the residual itself; a sublayer's result is multiplied by a learned sigmoid gate of the
              residual and the layer norm (weight and bias) comes after the sum, x <- LN(alpha x + gate * result); the mixer reads a
-             blend of the residual with the previous token's (token shift, carried per sequence) (blazr_b200/teselix.py).
+             blend of the residual with the previous token's (token shift, carried per sequence) (blazr_b200/teselix.py);
+  "out_norm": sublayers in sequence that read the residual itself; the RMS norm sits on the sublayer's OUTPUT, x <- x + norm(sublayer(x));
+             a mixer may be two branches side by side (an attention beside an element-wise gated recurrence) whose results are
+             summed with fixed scales or after a norm of their own; a hashed bigram table may join the embedding and the logits
+             may pass a soft cap (blazr_b200/pafelorn.py).
 The mechanisms are parameterised (window / chunk / pooled-block size, score scale, unit-norm epsilon, rotary table, gate, state
 size, activation kind, router groups, ...) so that another design can list them in another combination; a design is a function
 config.json -> LayeredConfig.
@@ -44,6 +48,10 @@ class RotarySpec:
     base: float
     yarn: Optional[tuple] = None
     layout: str = "interleaved"   # "interleaved": pairs (2i, 2i + 1); "half": pairs (i, i + dims / 2)
+    linear: float = 1.0           # every frequency is divided by this
+    # (factor, low, high, original): with wavelength l = 2 pi / f a frequency stays where l < original / high, is divided by factor where
+    # l > original / low, and in between is (1 - s) f / factor + s f with s = (original / l - low) / (high - low)
+    bands: Optional[tuple] = None
 
     def table(self):
         """(frequencies float32 [dims / 2], scale of cos and sin)"""
@@ -58,6 +66,13 @@ class RotarySpec:
             ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
             f = f / factor * ramp + f * (1.0 - ramp)
             mscale = 0.1 * math.log(factor) + 1.0
+        if self.bands is not None:
+            factor, low, high, original = self.bands
+            wl = 2.0 * math.pi / f
+            sm = (original / wl - low) / (high - low)
+            f = np.where(wl < original / high, f, np.where(wl > original / low, f / factor, (1.0 - sm) * f / factor + sm * f))
+        if self.linear != 1.0:
+            f = f / self.linear
         return f.astype(np.float32), float(mscale)
 
 
@@ -75,6 +90,17 @@ class AttentionSpec:
     pool: int = 0            # > 0 (with window): blocks of `pool` positions wholly before the window are seen through their mean key / value
     values_from_keys: bool = False   # no value projection: v = k as projected (before norm and rotation)
     rot: Optional[RotarySpec] = None
+    # ---- layout "out_norm" -------------------------------------------------------------------------------------------------------------
+    qk_norm: str = "none"    # weighted RMS norm of q and k before rotation: "head" (per head, one weight [dim] for all heads) | "full" (over the whole projection)
+    bias: bool = False       # q, k, v projections have biases
+    out_bias: bool = False   # so has the output projection
+    softcap: float = 0.0     # > 0: score <- softcap * tanh(score / softcap)
+    head_temp: bool = False  # one learned factor per head on the scores
+    sink: bool = False       # one learned logit per head joins the soft-max denominator (no key, no value)
+    keep_first: int = 0      # with a window: the first positions of a sequence stay visible
+    diff: Optional[float] = None   # differential attention: two maps per head over the same values, o = unit_rms(a1 - lambda a2) * (1 - diff)
+    gate_elem: bool = False  # with gated: the sigmoid gate has one logit per output element (heads * vdim) instead of one per head
+    kv_from: Optional[int] = None  # the keys and values are those of this (earlier) layer's cache; no k / v tensors of its own
 
 
 @dataclass
@@ -117,12 +143,43 @@ class LatentAttentionSpec:
 
 
 @dataclass
+class MinGruSpec:
+    """element-wise gated recurrence whose gates read only the current token: z = sigmoid(W_z h + b), u = W_x h + b, candidate u + 1/2 (u >= 0) or
+    sigmoid(u); S_t = (1 - z) S_(t-1) + z candidate; output W_o (S_t * silu(W_g h)); f32 state per sequence"""
+    width: int
+
+
+@dataclass
+class RgLruSpec:
+    """recurrent block with a real-gated linear recurrent unit: y = gelu_tanh(W_y h + b), u = causal_conv(W_x h + b); per block of width / blocks
+    channels r = sigmoid(A_r u + b), i = sigmoid(A_i u + b); a = exp(-decay * r * softplus(lam)); S_t = a S_(t-1) + sqrt(1 - a^2) i u;
+    output W_o (S_t * y); f32 state and the last conv - 1 convolution inputs per sequence"""
+    width: int
+    blocks: int
+    conv: int
+    decay: float = 8.0
+
+
+@dataclass
+class TwoBranchSpec:
+    """an attention (left) and a recurrence (right) read the same input; result = left_scale * left + right_scale * right, each branch first
+    RMS-normed over the model width with a weight of its own when branch_norm"""
+    left: AttentionSpec
+    right: object            # MinGruSpec | RgLruSpec
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    branch_norm: bool = False
+
+
+@dataclass
 class DenseFfSpec:
     ff: int
     limit: float = 0.0
     alpha: float = 1.702     # gate activation g * sigmoid(alpha * g)
     up_shift: float = 1.0    # (up + up_shift)
-    act: str = "swish_clamp" # "swish_clamp": min(g, limit) * sigmoid(alpha * g) * (clamp(up) + up_shift); "gelu_tanh": gelu_tanh(g) * up
+    # "swish_clamp": min(g, limit) * sigmoid(alpha * g) * (clamp(up) + up_shift); "gelu_tanh": gelu_tanh(g) * up;
+    # "polynorm" (no gate projection): c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 with z = W_up h and N the division by the row's root mean square
+    act: str = "swish_clamp"
 
 
 @dataclass
@@ -139,7 +196,11 @@ class MoeFfSpec:
     act: str = "relu2"       # a plain kind: down(act(up h)); a gated kind ("swish_clamp"): down(act(gate h, up h)) with limit / alpha / up_shift
     shared_ff: int = 0       # 0: no shared expert
     shared_gate: bool = True
-    router: str = "sigmoid"  # "sigmoid": learned router as above; "table": no router, a table [vocab, top] indexed by the token id names the experts, each weighted 1 / top
+    # "sigmoid": learned router as above; "table": no router, a table [vocab, top] indexed by the token id names the experts, each weighted 1 / top;
+    # "softmax": scores = soft-max over all router outputs, the choice adds a learned correction per output, the weights are the chosen scores normalised
+    router: str = "sigmoid"
+    identity: int = 0        # router "softmax": this many router outputs behind the experts' are identity experts (output = input, no tensors)
+    correction: bool = False # router "softmax": tensor "correction" [experts + identity] joins the choice
     limit: float = 0.0
     alpha: float = 1.702
     up_shift: float = 1.0
@@ -148,7 +209,7 @@ class MoeFfSpec:
 
 @dataclass
 class LayerSpec:
-    kind: str                # "attention" | "ssm" | "retention" | "latent_attention"
+    kind: str                # "attention" | "ssm" | "retention" | "latent_attention" | "two_branch"
     mixer: object
     ff: Optional[object]     # DenseFfSpec | MoeFfSpec | None
     weights_of: Optional[int] = None   # layout "post": the layer has no tensors of its own and uses those of this (earlier) layer, with its own cache / state
@@ -169,6 +230,8 @@ class LayeredConfig:
     tied_head: bool = True   # the output projection is the embedding table; False: a tensor "head"
     depth_average: bool = True   # layout "depth": layer i has weights "l<i>.dwa" [i + 2] over the embedding and the results of layers 0..i
     post_alpha: float = 1.0      # layout "post": weight of the residual in the sum that is normed
+    bigram: Optional[tuple] = None   # layout "out_norm": (buckets, mul_prev, mul_cur) of the hashed bigram table "bigram" [buckets + 1, width]
+    logit_softcap: float = 0.0       # > 0: logits <- cap * tanh(logits / cap)
 
 
 class _Workspace:
@@ -207,6 +270,13 @@ class _Workspace:
             self.oup = torch.empty((cap, max(1, model.max_inner)), **act)
             self.ff_inner = torch.empty((cap, max(1, model.max_ff_inner)), **act)
             self.ff_proj = torch.empty((cap, max(1, model.max_ff_proj)), **f32)
+        if cfg.layout == "out_norm":    # second branch of a two-branch mixer, the recurrences' intermediates, the feed-forward's own buffers
+            self.y2 = torch.empty((cap, W), **f32)
+            self.inner_b = torch.empty((cap, max(1, model.max_rinner)), **act)
+            self.conv_a = torch.empty((cap, max(1, model.max_xbc)), **act)
+            self.gates = torch.empty((cap, 2 * max(1, model.max_xbc)), **f32)
+            self.ff_inner = torch.empty((cap, max(1, model.max_ff_inner)), **act)
+            self.ff_proj = torch.empty((cap, max(1, model.max_ff_proj)), **f32)
         mo = model.moe_dims
         if mo is not None:              # mixture of experts: router logits, choices, sort, per-pair intermediates
             E1, top, F = mo
@@ -232,11 +302,11 @@ class _Workspace:
                                          order=torch.empty(n, **i32), slot=torch.empty(n, **i32))
         self.scratch = torch.empty(max(1, model.scratch_floats(cap)), **f32)      # work area: segmented state-space scan, key-split attention
         self.next_ids = torch.empty((cap,), dtype=torch.int32, device=dev)
-        # int32 step arrays in one buffer: ids | ent | pos | want | start | slot | pos0 | block_table
+        # int32 step arrays in one buffer: ids | ent | pos | want | start | slot | pos0 | prev | block_table
         B, mb = model.max_seqs, model.max_blocks
         self.off = {}
         o = 0
-        for k, n in (("ids", cap), ("ent", cap), ("pos", cap), ("want", cap), ("start", B + 1), ("slot", B), ("pos0", B), ("bt", B * mb)):
+        for k, n in (("ids", cap), ("ent", cap), ("pos", cap), ("want", cap), ("start", B + 1), ("slot", B), ("pos0", B), ("prev", B), ("bt", B * mb)):
             self.off[k] = (o, n)
             o += -(-n // 4) * 4
         self.meta = torch.zeros(o, dtype=torch.int32, device=dev)
@@ -280,10 +350,10 @@ class LayeredModel:
         def hc(pre):    # (in [S], post = out [S] | mix [S, S])
             return vec(pre + "in"), torch.cat([get(pre + "out").float().reshape(-1), get(pre + "mix").float().reshape(-1)]).contiguous().to(dev)
 
-        if cfg.layout not in ("streams", "depth", "post"):
+        if cfg.layout not in ("streams", "depth", "post", "out_norm"):
             raise ValueError(f"unknown residual layout {cfg.layout}")
-        depth, post = cfg.layout == "depth", cfg.layout == "post"
-        if (depth or post) and (S != 1 or cfg.canon_taps > 1):
+        depth, post, outn = cfg.layout == "depth", cfg.layout == "post", cfg.layout == "out_norm"
+        if (depth or post or outn) and (S != 1 or cfg.canon_taps > 1):
             raise ValueError("the depth-averaged and post-norm layouts have one residual stream and no carried convolution")
         self.embed = lin("embed")
         self.head = self.embed if cfg.tied_head else lin("head")
@@ -292,16 +362,27 @@ class LayeredModel:
         if tuple(self.embed.shape) != (cfg.vocab, W) or tuple(self.head.shape) != (cfg.vocab, W) or self.final_norm.numel() != W:
             raise ValueError("embedding / head / final norm shapes do not fit the configuration")
         self.ones_in = torch.ones(S, dtype=torch.float32, device=dev)
+        self.bigram = None
+        if cfg.bigram is not None:
+            if not outn:
+                raise ValueError("the bigram table is wired into the out_norm layout")
+            self.bigram = lin("bigram")
+            if tuple(self.bigram.shape) != (int(cfg.bigram[0]) + 1, W) or int(cfg.bigram[0]) < 1:
+                raise ValueError("the bigram table has buckets + 1 rows of the model width")
         self.layers: List[Dict[str, object]] = []
+        self.max_rinner = 1      # out_norm layout: widest recurrent branch
         self.max_proj = self.max_xbc = self.max_inner = 1
         self.max_ff_inner = self.max_ff_proj = 1      # depth layout: sizes of the feed-forward branch's own intermediates
         self.moe_dims = None      # (experts + 1, top, expert ff): largest over the layers
         self.max_q = self.max_qp = self.max_qn = 1      # latent attention: query rows, latent-space query rows, unrotated query parts
         self.max_ctx_r = self.max_ctx_kv = 0            # latent attention: latent size, per-head keys | values of one position
-        self.weight_bytes = self.embed.numel() * 2 + (0 if cfg.tied_head else self.head.numel() * 2)
+        self.weight_bytes = self.embed.numel() * 2 + (0 if cfg.tied_head else self.head.numel() * 2) + (self.bigram.numel() * 2 if self.bigram is not None else 0)
         for i, ls in enumerate(cfg.layers):
             if post:
                 self.layers.append(self._post_layer(i, ls, lin, vec, get))
+                continue
+            if outn:
+                self.layers.append(self._out_layer(i, ls, lin, vec, get))
                 continue
             L: Dict[str, object] = {"spec": ls}
             p = f"l{i}."
@@ -488,36 +569,7 @@ class LayeredModel:
             return gu.view(2, ff, W).transpose(0, 1).reshape(2 * ff, W).contiguous()
 
         if isinstance(f, MoeFfSpec):
-            if f.act not in seqops.ACT_KINDS or not 1 <= f.top <= f.experts:
-                raise ValueError(f"layer {i}: expert activation {f.act} / top {f.top} is not supported")
-            gated = seqops.ACT_KINDS[f.act] in seqops.ACT_GATED
-            if f.router == "table":
-                t = get(p + "mlp.table")
-                if t.dtype not in (torch.int32, torch.int64) or tuple(t.shape) != (cfg.vocab, f.top):
-                    raise ValueError(f"layer {i}: the expert table is an integer tensor [vocab, top]")
-                if int(t.min()) < 0 or int(t.max()) >= f.experts:
-                    raise ValueError(f"layer {i}: the expert table names an expert outside 0..{f.experts - 1}")
-                L["table"] = t.to(torch.int32).contiguous().to(dev)
-            elif f.router == "sigmoid":
-                router = [p + "mlp.router"] + ([p + "mlp.shared.sg"] if f.shared_ff and f.shared_gate else [])
-                L["w_router"] = lin(*router)
-                self.weight_bytes += L["w_router"].numel() * 2
-            else:
-                raise ValueError(f"layer {i}: unknown router kind {f.router}")
-            if gated:
-                L["w_eup"] = torch.stack([gate_up(p + f"mlp.e{e}.", f.ff) for e in range(f.experts)]).contiguous()
-            else:
-                L["w_eup"] = torch.stack([lin(p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
-            L["w_edown"] = torch.stack([lin(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
-            if tuple(L["w_eup"].shape[1:]) != ((2 if gated else 1) * f.ff, W) or tuple(L["w_edown"].shape[1:]) != (W, f.ff):
-                raise ValueError(f"layer {i}: expert tensor shapes do not fit the configuration")
-            self.weight_bytes += (L["w_eup"].numel() + L["w_edown"].numel()) * 2
-            if f.shared_ff:
-                L["w_sup"] = gate_up(p + "mlp.shared.", f.shared_ff) if gated else lin(p + "mlp.shared.up")
-                L["w_sdown"] = lin(p + "mlp.shared.down")
-                if L["w_sup"].shape[1] != W or tuple(L["w_sdown"].shape) != (W, f.shared_ff):
-                    raise ValueError(f"layer {i}: shared expert tensor shapes do not fit the configuration")
-                self.weight_bytes += (L["w_sup"].numel() + L["w_sdown"].numel()) * 2
+            self._load_moe(L, i, f, lin, vec, get)
         elif f is not None:
             if f.act not in seqops.ACT_KINDS or seqops.ACT_KINDS[f.act] not in seqops.ACT_GATED:
                 raise ValueError(f"layer {i}: dense feed-forward activation {f.act} is not a gated kind")
@@ -528,6 +580,217 @@ class LayeredModel:
             self.weight_bytes += (L["w_gu"].numel() + L["w_down"].numel()) * 2
         self._post_sizes(L, ls)
         return L
+
+    # ---- layout "out_norm": weights of one layer ------------------------------------------------------------------------------------------
+    def _out_layer(self, i: int, ls: "LayerSpec", lin, vec, get) -> Dict[str, object]:
+        """One stacked input projection per mixer: [q | k | v | gate] of the attention, then the recurrent branch's projections; the biases of the
+        projections form one f32 vector indexed by the stacked row's columns (zero where a projection has none), added by the kernels that read the row."""
+        import math
+        cfg, dev, W = self.cfg, self.dev, self.cfg.width
+        L: Dict[str, object] = {"spec": ls}
+        p = f"l{i}."
+        L["norm1"] = vec(p + "norm1")
+        if L["norm1"].numel() != W:
+            raise ValueError(f"layer {i}: norm weight does not fit the width")
+        if ls.kind == "attention":
+            att, right, ap = ls.mixer, None, p + "mix."
+        elif ls.kind == "two_branch":
+            att, right, ap = ls.mixer.left, ls.mixer.right, p + "mix.left."
+        else:
+            raise ValueError(f"layer {i}: mixer kind {ls.kind} is not wired into the out_norm layout")
+        m = att
+        H, G, D, V = m.heads, m.kv_heads, m.dim, m.vdim
+        if H % G or m.values_from_keys or m.pool or m.chunk:
+            raise ValueError(f"layer {i}: attention options that this layout does not wire (or heads not a multiple of kv_heads)")
+        maps = 2 if m.diff is not None else 1
+        shared = m.kv_from is not None
+        if shared:
+            j = m.kv_from
+            src = cfg.layers[j] if 0 <= j < i else None
+            sm = None if src is None else (src.mixer if src.kind == "attention" else src.mixer.left if src.kind == "two_branch" else None)
+            if sm is None or sm.kv_from is not None or (sm.heads, sm.kv_heads, sm.dim, sm.vdim, sm.diff is None) != (H, G, D, V, m.diff is None):
+                raise ValueError(f"layer {i}: kv_from must name an earlier attention layer with keys of its own and the same head counts and sizes")
+        parts, biases = [], []
+
+        def add(name, rows, bias, perm=None):
+            t = get(name)
+            if tuple(t.shape) != (rows, W):
+                raise ValueError(f"layer {i}: {name} has shape {tuple(t.shape)}, expected {(rows, W)}")
+            b = get(name + ".b").float().reshape(-1) if bias else torch.zeros(rows)
+            if b.numel() != rows:
+                raise ValueError(f"layer {i}: {name}.b does not fit")
+            if perm is not None:
+                t, b = perm(t), perm(b)
+            parts.append(t.to(torch.bfloat16) if t.dtype != torch.bfloat16 else t)
+            biases.append(b)
+
+        # differential attention: the query rows come head by head as [map 1 | map 2]; they are reordered to [key group][map][head of the group] so
+        # that the two maps are 2 H plain query heads over 2 G key heads (query head h' reads key head h' / (H / G)) that share G value heads
+        R = H // G
+        qperm = (lambda t: t.reshape(G, R, 2, D, *t.shape[1:]).transpose(1, 2).reshape(t.shape)) if maps == 2 else None
+        add(ap + "q", H * maps * D, m.bias, qperm)
+        if not shared:
+            add(ap + "k", G * maps * D, m.bias)
+            add(ap + "v", G * V, m.bias)
+        if m.gated:
+            add(ap + "g", H * V if m.gate_elem else H, False)
+        n_att = sum(t.shape[0] for t in parts)
+        rc = {}
+        if isinstance(right, MinGruSpec):
+            C = right.width
+            for nm, b in (("z", True), ("x", True), ("g", False)):
+                rc[nm] = sum(t.shape[0] for t in parts)
+                add(p + "mix.right." + nm, C, b)
+        elif isinstance(right, RgLruSpec):
+            C = right.width
+            if right.blocks < 1 or C % right.blocks or not 1 <= right.conv <= 8:
+                raise ValueError(f"layer {i}: blocks must divide the recurrent width, 1..8 convolution taps")
+            for nm in ("y", "x"):
+                rc[nm] = sum(t.shape[0] for t in parts)
+                add(p + "mix.right." + nm, C, True)
+        elif right is not None:
+            raise ValueError(f"layer {i}: unknown recurrent branch {type(right).__name__}")
+        L["w_in"] = torch.cat(parts, 0).contiguous().to(dev)
+        bias = torch.cat(biases).to(torch.float32)
+        L["in_bias"] = bias.contiguous().to(dev) if bool((bias != 0).any()) else None
+        L["w_o"] = lin(ap + "o")
+        if tuple(L["w_o"].shape) != (W, H * V):
+            raise ValueError(f"layer {i}: output projection shape does not fit")
+        L["o_bias"] = vec(ap + "o.b") if m.out_bias else None
+        self.weight_bytes += (L["w_in"].numel() + L["w_o"].numel()) * 2
+        rot_freq, rot_scale = None, 1.0
+        if m.rot is not None:
+            if m.rot.dims < 2 or m.rot.dims % 2 or m.rot.dims > D or m.rot.layout not in ("half", "interleaved"):
+                raise ValueError(f"layer {i}: rotary dimensions must be even and at most the head size, layout half or interleaved")
+            fr, rot_scale = m.rot.table()
+            rot_freq = torch.from_numpy(fr).to(dev)
+        L["rot_freq"] = rot_freq
+        if m.qk_norm not in ("none", "head", "full"):
+            raise ValueError(f"layer {i}: unknown q / k norm {m.qk_norm}")
+        L["q_norm_w"] = vec(ap + "q.norm") if m.qk_norm != "none" else None
+        L["k_norm_w"] = vec(ap + "k.norm") if m.qk_norm != "none" and not shared else None
+        nq, nk = (D, D) if m.qk_norm == "head" else (H * maps * D, G * maps * D)
+        if L["q_norm_w"] is not None and (L["q_norm_w"].numel() != nq or (L["k_norm_w"] is not None and L["k_norm_w"].numel() != nk)):
+            raise ValueError(f"layer {i}: q / k norm weights do not fit")
+        if m.qk_norm == "full" and maps == 2:
+            raise ValueError(f"layer {i}: a norm over the whole projection is not wired for differential attention")
+        L["temp"] = vec(ap + "temp") if m.head_temp else None
+        L["sink"] = vec(ap + "sink") if m.sink else None
+        if (L["temp"] is not None and L["temp"].numel() != H) or (L["sink"] is not None and L["sink"].numel() != H) or (maps == 2 and (m.head_temp or m.sink)):
+            raise ValueError(f"layer {i}: one temperature / sink per head (not with differential attention)")
+        L["desc"] = seqops.attn_desc(H * maps, G * maps, D, V, m.scale, gated=m.gated, gate_elem=m.gate_elem, window=m.window,
+                                     qk_eps=cfg.eps if (m.qk_norm != "none" or m.qk_unit_norm) else -1.0, rot_freq=rot_freq, rot_scale=rot_scale, sink=L["sink"],
+                                     q_norm_w=L["q_norm_w"], k_norm_w=L["k_norm_w"], norm_full=m.qk_norm == "full", rot_half=m.rot is not None and m.rot.layout == "half",
+                                     in_bias=L["in_bias"], kv_shared=shared, value_heads=G if maps == 2 else 0, softcap=m.softcap, head_scale=L["temp"],
+                                     keep_first=m.keep_first if m.window > 0 else 0)
+        if L["desc"].width != n_att:
+            raise AssertionError("attention columns of the stacked projection")
+        if maps == 2:
+            for nm in ("lq1", "lk1", "lq2", "lk2"):
+                if get(ap + nm).numel() != D:
+                    raise ValueError(f"layer {i}: {nm} has the head size")
+            f64 = lambda nm: get(ap + nm).to(torch.float64).reshape(-1)
+            L["lambda"] = float(torch.exp((f64("lq1") * f64("lk1")).sum()) - torch.exp((f64("lq2") * f64("lk2")).sum())) + float(m.diff)
+        self.max_inner = max(self.max_inner, H * V * maps)
+        L["rcols"] = rc
+        if isinstance(right, MinGruSpec):
+            L["w_ro"] = lin(p + "mix.right.o")
+        elif isinstance(right, RgLruSpec):
+            C, nb = right.width, right.blocks
+            bw = C // nb
+            L["w_ro"] = lin(p + "mix.right.o")
+            L["conv_w"], L["conv_b"] = vec(p + "mix.right.conv"), vec(p + "mix.right.conv.b")
+            ra, ri = get(p + "mix.right.ra"), get(p + "mix.right.ri")
+            if tuple(ra.shape) != (nb, bw, bw) or tuple(ri.shape) != (nb, bw, bw) or tuple(L["conv_w"].shape) != (C, right.conv) or L["conv_b"].numel() != C:
+                raise ValueError(f"layer {i}: recurrent gate / convolution tensor shapes do not fit")
+            L["w_gates"] = torch.cat([ra.to(torch.bfloat16), ri.to(torch.bfloat16)], 1).contiguous().to(dev)      # [blocks][r rows | i rows][bw]
+            L["gate_bias"] = torch.cat([get(p + "mix.right.ra.b").float().reshape(nb, bw), get(p + "mix.right.ri.b").float().reshape(nb, bw)], 1).reshape(-1).contiguous().to(dev)
+            lam = get(p + "mix.right.lam").to(torch.float64).reshape(-1)
+            if lam.numel() != C:
+                raise ValueError(f"layer {i}: lam has the recurrent width")
+            L["sp_lam"] = torch.nn.functional.softplus(lam).to(torch.float32).contiguous().to(dev)
+            L["x_bias"] = L["in_bias"][rc["x"]:rc["x"] + C] if L["in_bias"] is not None else None
+            self.max_xbc = max(self.max_xbc, C)
+            self.weight_bytes += L["w_gates"].numel() * 2
+        if right is not None:
+            if tuple(L["w_ro"].shape) != (W, right.width):
+                raise ValueError(f"layer {i}: recurrent output projection shape does not fit")
+            self.max_rinner = max(self.max_rinner, right.width)
+            self.weight_bytes += L["w_ro"].numel() * 2
+            if ls.mixer.branch_norm:
+                L["left_out"], L["right_out"] = vec(p + "mix.left.out"), vec(p + "mix.right.out")
+                if L["left_out"].numel() != W or L["right_out"].numel() != W:
+                    raise ValueError(f"layer {i}: branch norm weights do not fit the width")
+        self.max_proj = max(self.max_proj, L["w_in"].shape[0])
+        f = ls.ff
+        if f is not None:
+            L["norm2"] = vec(p + "norm2")
+            if L["norm2"].numel() != W:
+                raise ValueError(f"layer {i}: norm weight does not fit the width")
+        if isinstance(f, MoeFfSpec):
+            self._load_moe(L, i, f, lin, vec, get)
+        elif f is not None:
+            if f.act != "polynorm":
+                raise ValueError(f"layer {i}: dense feed-forward activation {f.act} is not wired into the out_norm layout")
+            L["w_up"], L["w_down"], L["act_coef"] = lin(p + "mlp.up"), lin(p + "mlp.down"), vec(p + "mlp.act")
+            if tuple(L["w_up"].shape) != (f.ff, W) or tuple(L["w_down"].shape) != (W, f.ff) or L["act_coef"].numel() != 4:
+                raise ValueError(f"layer {i}: feed-forward tensor shapes do not fit the configuration")
+            self.weight_bytes += (L["w_up"].numel() + L["w_down"].numel()) * 2
+            self.max_ff_inner, self.max_ff_proj = max(self.max_ff_inner, f.ff), max(self.max_ff_proj, f.ff)
+        return L
+
+    def _load_moe(self, L, i: int, f: "MoeFfSpec", lin, vec, get) -> None:
+        """tensors of a mixture-of-experts feed-forward: router (rows of a shared expert's token gate stacked behind it) or table, stacked expert
+        weights (gated kinds with alternating gate / up rows), the shared expert"""
+        cfg, W, p = self.cfg, self.cfg.width, f"l{i}."
+        if f.act not in seqops.ACT_KINDS or not 1 <= f.top <= f.experts + f.identity:
+            raise ValueError(f"layer {i}: expert activation {f.act} / top {f.top} is not supported")
+        gated = seqops.ACT_KINDS[f.act] in seqops.ACT_GATED
+
+        def gate_up(pre, ff):      # rows alternate (gate j, up j): the pair meets in one warp / neighbouring lanes
+            gu = lin(pre + "gate", pre + "up")
+            if tuple(gu.shape) != (2 * ff, W):
+                raise ValueError(f"layer {i}: {pre}gate / up shapes do not fit the configuration")
+            return gu.view(2, ff, W).transpose(0, 1).reshape(2 * ff, W).contiguous()
+
+        if f.router == "table":
+            t = get(p + "mlp.table")
+            if t.dtype not in (torch.int32, torch.int64) or tuple(t.shape) != (cfg.vocab, f.top):
+                raise ValueError(f"layer {i}: the expert table is an integer tensor [vocab, top]")
+            if int(t.min()) < 0 or int(t.max()) >= f.experts:
+                raise ValueError(f"layer {i}: the expert table names an expert outside 0..{f.experts - 1}")
+            L["table"] = t.to(torch.int32).contiguous().to(self.dev)
+        elif f.router in ("sigmoid", "softmax"):
+            if f.router == "sigmoid" and (f.identity or f.correction):
+                raise ValueError(f"layer {i}: identity experts and a correction go with the soft-max router")
+            router = [p + "mlp.router"] + ([p + "mlp.shared.sg"] if f.shared_ff and f.shared_gate else [])
+            L["w_router"] = lin(*router)
+            if tuple(L["w_router"].shape) != (len(router) - 1 + f.experts + f.identity, W):
+                raise ValueError(f"layer {i}: router shape does not fit the configuration")
+            self.weight_bytes += L["w_router"].numel() * 2
+            L["correction"] = vec(p + "mlp.correction") if f.correction else None
+            if L["correction"] is not None and L["correction"].numel() != f.experts + f.identity:
+                raise ValueError(f"layer {i}: one correction per router output expected")
+        else:
+            raise ValueError(f"layer {i}: unknown router kind {f.router}")
+        if gated:
+            L["w_eup"] = torch.stack([gate_up(p + f"mlp.e{e}.", f.ff) for e in range(f.experts)]).contiguous()
+        else:
+            L["w_eup"] = torch.stack([lin(p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
+        L["w_edown"] = torch.stack([lin(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
+        if tuple(L["w_eup"].shape[1:]) != ((2 if gated else 1) * f.ff, W) or tuple(L["w_edown"].shape[1:]) != (W, f.ff):
+            raise ValueError(f"layer {i}: expert tensor shapes do not fit the configuration")
+        self.weight_bytes += (L["w_eup"].numel() + L["w_edown"].numel()) * 2
+        if f.shared_ff:
+            L["w_sup"] = gate_up(p + "mlp.shared.", f.shared_ff) if gated else lin(p + "mlp.shared.up")
+            L["w_sdown"] = lin(p + "mlp.shared.down")
+            if L["w_sup"].shape[1] != W or tuple(L["w_sdown"].shape) != (W, f.shared_ff):
+                raise ValueError(f"layer {i}: shared expert tensor shapes do not fit the configuration")
+            self.weight_bytes += (L["w_sup"].numel() + L["w_sdown"].numel()) * 2
+            self.max_ff_inner = max(self.max_ff_inner, f.shared_ff)
+            self.max_ff_proj = max(self.max_ff_proj, 2 * f.shared_ff)
+        md = self.moe_dims or (1, 1, 1)
+        self.moe_dims = (max(md[0], f.experts + f.identity + 1), max(md[1], f.top), max(md[2], f.ff))
 
     def _post_sizes(self, L, ls: "LayerSpec") -> None:
         """largest intermediates over the layers (workspace sizes)"""
@@ -568,6 +831,19 @@ class LayeredModel:
                     L["canon2_state"] = torch.zeros((max_seqs, max(hist, 1), cfg.width), **f32)
             if cfg.layout == "post":
                 L["shift_state"] = torch.zeros((max_seqs, cfg.width), **f32)      # the mixer input of the sequence's last token
+            if cfg.layout == "out_norm":
+                att = m if ls.kind == "attention" else m.left
+                maps = 2 if att.diff is not None else 1
+                if att.kv_from is None:      # a layer that reads another layer's keys and values has no pool (bound below, when all pools exist)
+                    L["kpool"] = torch.zeros((max(1, num_blocks), block_size, att.kv_heads * maps, att.dim), **f32)
+                    L["vpool"] = torch.zeros((max(1, num_blocks), block_size, att.kv_heads, att.vdim), **f32)
+                right = None if ls.kind == "attention" else m.right
+                if isinstance(right, MinGruSpec):
+                    L["rec_state"] = torch.zeros((max_seqs, right.width), **f32)
+                elif isinstance(right, RgLruSpec):
+                    L["rec_state"] = torch.zeros((max_seqs, right.width), **f32)
+                    L["conv_state"] = torch.zeros((max_seqs, max(right.conv - 1, 1), right.width), **f32)
+                continue
             if ls.kind == "retention":
                 L["ret_state"] = torch.zeros((max_seqs, m.heads, m.dim, m.vdim), **f32)
             elif ls.kind == "latent_attention":       # one row [latent | rotated key part] per position; keys and values of all heads come out of it
@@ -584,6 +860,10 @@ class LayeredModel:
             else:
                 L["conv_state"] = torch.zeros((max_seqs, max(m.conv - 1, 1), m.heads * m.vdim + 2 * m.groups * m.state), **f32)
                 L["ssm_state"] = torch.zeros((max_seqs, m.heads, m.state, m.vdim), **f32)
+        if cfg.layout == "out_norm":
+            for L in self.layers:
+                att = L["spec"].mixer if L["spec"].kind == "attention" else L["spec"].mixer.left
+                L["kv_src"] = self.layers[att.kv_from] if att.kv_from is not None else L
         self._ws.clear()
         self._graphs.clear()
 
@@ -593,6 +873,17 @@ class LayeredModel:
         seen = set()
         for L in self.layers:
             m = L["spec"].mixer
+            if self.cfg.layout == "out_norm":
+                att = m if L["spec"].kind == "attention" else m.left
+                maps = 2 if att.diff is not None else 1
+                ctx = keys = self.max_blocks * self.block_size
+                if att.window > 0:
+                    keys = min(ctx, att.window + att.keep_first)
+                key = (att.heads * maps, att.kv_heads * maps, att.vdim, keys)
+                if key not in seen:
+                    seen.add(key)
+                    need = max([need] + [seqops.attn_scratch_floats(T, 1, key[0], key[1], att.vdim, keys) for T in range(1, cap + 1)])
+                continue
             if L["spec"].kind == "ssm":
                 need = max(need, seqops.ssm_scratch_floats(cap, self.max_seqs, m.heads, m.vdim, m.state))
             elif L["spec"].kind == "retention":
@@ -616,7 +907,7 @@ class LayeredModel:
         return need
 
     def cache_bytes(self) -> int:
-        keys = ("canon1_state", "canon2_state", "kpool", "vpool", "kpooled", "vpooled", "conv_state", "ssm_state", "shift_state", "ret_state")
+        keys = ("canon1_state", "canon2_state", "kpool", "vpool", "kpooled", "vpooled", "conv_state", "ssm_state", "shift_state", "ret_state", "rec_state")
         return sum(L[k].numel() * 4 for L in self.layers for k in keys if k in L)
 
     def _ctx_buffers(self, rows: int):
@@ -647,8 +938,9 @@ class LayeredModel:
         if ws.copied is not None:
             ws.copied.synchronize()    # the previous step's copy out of the pinned buffer must be over before it is rewritten
         hn = h.numpy()
+        prev = sa.ent_prev if sa.ent_prev is not None else np.zeros(sa.B, dtype=np.int32)
         for k, arr in (("ids", sa.tok_ids), ("ent", sa.tok_ent), ("pos", sa.tok_pos), ("want", sa.want_rows), ("start", sa.ent_start), ("slot", sa.ent_slot),
-                       ("pos0", sa.ent_pos0)):
+                       ("pos0", sa.ent_pos0), ("prev", prev)):
             o, _ = ws.off[k]
             hn[o:o + arr.shape[0]] = arr
         o, _ = ws.off["bt"]
@@ -703,10 +995,14 @@ class LayeredModel:
             self._run_depth(ws, T, B, R, sample, debug_layers)
         elif self.cfg.layout == "post":
             self._run_post(ws, T, B, R, debug_layers)
+        elif self.cfg.layout == "out_norm":
+            self._run_out(ws, T, B, R, debug_layers)
         else:
             self._run_streams(ws, T, B, R, sample, debug_layers)
         if R:
             seqops.linear(ws.fin[:R], self.head, ws.logits[:R])
+            if self.cfg.logit_softcap > 0:
+                seqops.softcap(ws.logits[:R], self.cfg.logit_softcap)
             if sample:
                 seqops.argmax(ws.logits[:R], ws.next_ids[:R])
 
@@ -858,6 +1154,84 @@ class LayeredModel:
         if R:
             ops.post_norm(x, self.final_norm, self.final_bias, cfg.eps, rows=ws.view("want")[:R], a_out=ws.fin[:R])
 
+    def _run_out(self, ws: _Workspace, T: int, B: int, R: int, debug_layers: Optional[list]) -> None:
+        """sublayers in sequence over one residual x (f32) that they read as it is; between sublayers ONE kernel sums the mixer's branches (with
+        their scales, output bias and branch norms), applies the norm on the sublayer's output, adds the residual and writes the next sublayer's
+        input in the activation type; after the last sublayer the same kernel applies the final norm to the wanted rows."""
+        cfg, ops = self.cfg, seqops
+        st = self._desc(ws, T, B)
+        x, a, y, y2 = ws.h[:T], ws.a[:T], ws.y[:T], ws.y2[:T]
+        bg = cfg.bigram or (0, 0, 0)
+        ops.embed_bigram(self.embed, self.bigram, ws.view("ids"), ws.view("prev"), st, cfg.embed_scale, int(bg[0]), int(bg[1]), int(bg[2]), x, a)
+        n = len(self.layers)
+        want = ws.view("want")[:R]
+
+        def close(L, q, last, **branches):
+            """x <- x + norm_q(branches); the last sublayer of the model leaves the final norm of the wanted rows instead of the next input"""
+            if last and debug_layers is None:
+                if R:
+                    ops.branch_norm(x, w=L[f"norm{q}"], eps=cfg.eps, rows=want, a_out=ws.fin[:R], fin_w=self.final_norm, **branches)
+                return
+            ops.branch_norm(x, w=L[f"norm{q}"], eps=cfg.eps, x_out=x, a_out=a, **branches)
+
+        for i, L in enumerate(self.layers):
+            ls: LayerSpec = L["spec"]
+            proj = ws.proj[:T, :L["w_in"].shape[0]]
+            ops.linear(a, L["w_in"], proj)
+            has_ff = ls.ff is not None
+            last = i + 1 == n
+            if ls.kind == "attention":
+                self._attention_out(L, ls.mixer, ws, st, T, proj, y)
+                close(L, 1, last and not has_ff, y1=y, bias1=L["o_bias"])
+            else:
+                tb: TwoBranchSpec = ls.mixer
+                self._attention_out(L, tb.left, ws, st, T, proj, y)
+                self._recurrent_branch(L, tb.right, ws, st, T, proj, y2)
+                close(L, 1, last and not has_ff, y1=y, bias1=L["o_bias"], w_b1=L.get("left_out"), s1=tb.left_scale, y2=y2, w_b2=L.get("right_out"), s2=tb.right_scale)
+            if has_ff:
+                if isinstance(ls.ff, MoeFfSpec):
+                    self._moe_ff(L, ls.ff, ws, T, a, y, x_id=x)
+                else:
+                    z = ws.ff_proj.view(-1)[:T * ls.ff.ff].view(T, ls.ff.ff)
+                    ops.linear(a, L["w_up"], z)
+                    mid = ws.ff_inner.view(-1)[:T * ls.ff.ff].view(T, ls.ff.ff)
+                    ops.polynorm(z, L["act_coef"], cfg.eps, mid)
+                    ops.linear(mid, L["w_down"], y)
+                close(L, 2, last, y1=y)
+            if debug_layers is not None:
+                debug_layers.append(x.cpu())
+        if R and (not n or debug_layers is not None):
+            ops.group_rmsnorm(x if R == T and debug_layers is None else x.index_select(0, want.long()), self.final_norm, 1, cfg.eps, ws.fin[:R])
+
+    def _attention_out(self, L, m: AttentionSpec, ws: _Workspace, st, T: int, proj: torch.Tensor, y: torch.Tensor) -> None:
+        """attention of the out_norm layout over the layer's own pool or the pool of the layer whose keys and values it shares"""
+        src = L["kv_src"]
+        seqops.attn_prep_ex(proj, st, L["desc"], L.get("kpool"), L.get("vpool"))
+        H, V = m.heads, m.vdim
+        o = ws.inner_a.view(-1)[:T * H * V].view(T, H * V)
+        if m.diff is not None:      # two maps per head as 2 H plain heads, f32; then o = unit_rms(a1 - lambda a2) * (1 - diff)
+            a12 = ws.inner_f.view(-1)[:T * 2 * H * V].view(T, 2 * H * V)
+            seqops.attn_ex(proj, st, L["desc"], src["kpool"], src["vpool"], a12, ws.scratch)
+            seqops.diff_combine(a12, H, m.kv_heads, V, L["lambda"], 1.0 - m.diff, self.cfg.eps, o)
+        else:
+            seqops.attn_ex(proj, st, L["desc"], src["kpool"], src["vpool"], o, ws.scratch)
+        seqops.linear(o, L["w_o"], y)
+
+    def _recurrent_branch(self, L, r, ws: _Workspace, st, T: int, proj: torch.Tensor, y: torch.Tensor) -> None:
+        rc, C = L["rcols"], r.width
+        out = ws.inner_b.view(-1)[:T * C].view(T, C)
+        if isinstance(r, MinGruSpec):
+            seqops.min_gru(proj, rc["z"], rc["x"], rc["g"], L["in_bias"], L["rec_state"], st, C, out)
+        else:
+            u = ws.xbc.view(-1)[:T * C].view(T, C)
+            ua = ws.conv_a.view(-1)[:T * C].view(T, C)
+            seqops.causal_conv_ex(proj[:, rc["x"]:rc["x"] + C], L["x_bias"], L["conv_w"], L["conv_b"], L["conv_state"], st, 0, u, ua)
+            gates = ws.gates.view(-1)[:T * 2 * C].view(T, 2 * C)
+            bw = C // r.blocks
+            seqops.head_linear(ua, L["w_gates"], gates, 2 * bw)
+            seqops.rg_lru(u, gates, L["gate_bias"], L["sp_lam"], r.decay, proj, rc["y"], L["in_bias"], L["rec_state"], st, r.blocks, out)
+        seqops.linear(out, L["w_ro"], y)
+
     def _retention(self, L, m: RetentionSpec, ws: _Workspace, st, T: int, a: torch.Tensor, y: torch.Tensor) -> None:
         proj = ws.proj[:T, :L["w_in"].shape[0]]
         seqops.linear(a, L["w_in"], proj)
@@ -981,11 +1355,11 @@ class LayeredModel:
 
     MOE_ROW_PAIRS = 64      # up to this many (token, choice) pairs the experts' weights are streamed per pair; more: tiles over sorted pairs
 
-    def _moe_ff(self, L, f: "MoeFfSpec", ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor, shared_done=None, route=None) -> None:
+    def _moe_ff(self, L, f: "MoeFfSpec", ws: _Workspace, T: int, a: torch.Tensor, y: torch.Tensor, shared_done=None, route=None, x_id=None) -> None:
         """shared_done: event after which the shared expert's output is in ws.moe_sh (it ran elsewhere); None: it runs here.
         route: the layer's own choice buffers, filled (and sorted) earlier in the step (table-routed layers); None: the choice is made here"""
         ops = seqops
-        E, top = f.experts, f.top
+        E, top = f.experts + f.identity, f.top      # E: router outputs (identity experts behind the real ones: they take part in the choice and the sort)
         gated_shared = bool(f.shared_ff and f.shared_gate)
         pairs = T * top
         rows_form = pairs <= self.MOE_ROW_PAIRS
@@ -995,6 +1369,10 @@ class LayeredModel:
             pass
         elif f.router == "table":         # no router: the token id names the experts
             ops.moe_table_route(L["table"], ws.view("ids"), T, E, top, ids, wts, None if rows_form else ws.moe_cnt)
+        elif f.router == "softmax":
+            z = ws.moe_z[:T, :L["w_router"].shape[0]]
+            ops.linear(a, L["w_router"], z)
+            ops.moe_route_ex(z, E, 1, 1, top, ops.ROUTE_SOFTMAX, L["correction"], ids, wts, None if rows_form else ws.moe_cnt)
         else:
             z = ws.moe_z[:T, :L["w_router"].shape[0]]
             if T <= 8 and rows_form:        # few tokens: projection and choice in one kernel
@@ -1026,7 +1404,11 @@ class LayeredModel:
             sh = ws.moe_sh[:T]
         elif f.shared_ff:
             sh = self._shared_expert(L, f, ws, T, a)
-        ops.moe_combine(ys, wts, slot, T, top, sh, z[:, E] if gated_shared and z is not None else None, y)
+        gate_z = z[:, E] if gated_shared and z is not None else None
+        if f.identity:
+            ops.moe_combine_ex(ys, wts, slot, ids, f.experts, x_id, T, top, sh, gate_z, y)
+        else:
+            ops.moe_combine(ys, wts, slot, T, top, sh, gate_z, y)
 
     def _shared_expert(self, L, f: "MoeFfSpec", ws: _Workspace, T: int, a: torch.Tensor) -> torch.Tensor:
         smid = ws.ff_inner.view(-1)[:T * f.shared_ff].view(T, f.shared_ff)

@@ -12,7 +12,7 @@ from __future__ import annotations
 import os
 from typing import Callable, Dict
 
-from . import fenorax, gemosun, teselix
+from . import fenorax, gemosun, pafelorn, teselix
 from .layered import LayeredConfig, LayeredModel
 
 LAYERED: Dict[str, Callable[[dict], LayeredConfig]] = {}
@@ -25,6 +25,7 @@ def register_layered(name: str, parse: Callable[[dict], LayeredConfig]) -> None:
 
 register_layered(fenorax.ARCHITECTURE, fenorax.parse_config)
 register_layered(gemosun.ARCHITECTURE, gemosun.parse_config)
+register_layered(pafelorn.ARCHITECTURE, pafelorn.parse_config)
 register_layered(teselix.ARCHITECTURE, teselix.parse_config)
 
 

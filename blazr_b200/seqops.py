@@ -36,7 +36,9 @@ EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b20
            "b200seq_causal_conv", "b200seq_group_rmsnorm", "b200seq_gated_act", "b200seq_linear", "b200seq_linear_gated", "b200seq_attn_prep", "b200seq_attn", "b200seq_attn_scratch_floats",
            "b200seq_ssm_scan", "b200seq_ssm_scratch_floats", "b200seq_argmax", "b200seq_linear_act", "b200seq_act", "b200seq_depth_norm", "b200seq_attn_prep_ex",
            "b200seq_attn_ex", "b200seq_moe_route", "b200seq_moe_sort", "b200seq_moe_linear", "b200seq_moe_gather", "b200seq_moe_combine", "b200seq_moe_router", "b200seq_moe_table_route", "b200seq_moe_linear_act", "b200seq_head_linear", "b200seq_latent_gather",
-           "b200seq_latent_prep", "b200seq_rotary", "b200seq_retention", "b200seq_retention_scratch_floats", "b200seq_token_shift", "b200seq_post_norm"]
+           "b200seq_latent_prep", "b200seq_rotary", "b200seq_retention", "b200seq_retention_scratch_floats", "b200seq_token_shift", "b200seq_post_norm",
+           "b200seq_moe_route_ex", "b200seq_moe_combine_ex", "b200seq_causal_conv_ex", "b200seq_embed_bigram", "b200seq_branch_norm", "b200seq_polynorm", "b200seq_softcap",
+           "b200seq_diff_combine", "b200seq_min_gru", "b200seq_rg_lru"]
 
 
 class SeqError(RuntimeError):
@@ -55,7 +57,9 @@ class AttnDesc(C.Structure):
     """b200seq_attn_desc: sizes, columns of the projection row and mask / rotation constants of one attention layer"""
     _fields_ = [("H", C.c_int32), ("G", C.c_int32), ("D", C.c_int32), ("V", C.c_int32), ("q_col", C.c_int32), ("k_col", C.c_int32), ("v_col", C.c_int32),
                 ("gate_col", C.c_int32), ("scale", C.c_float), ("chunk", C.c_int32), ("window", C.c_int32), ("pool", C.c_int32), ("qk_eps", C.c_float),
-                ("rot_dims", C.c_int32), ("rot_freq", C.c_void_p), ("rot_scale", C.c_float), ("sink", C.c_void_p), ("latent_v", C.c_int32), ("gate", C.c_void_p), ("gate_ld", C.c_int64), ("ctx_rows", C.c_int32), ("kd", C.c_int32), ("kv_ld", C.c_int64), ("krot", C.c_void_p), ("krot_ld", C.c_int64)]
+                ("rot_dims", C.c_int32), ("rot_freq", C.c_void_p), ("rot_scale", C.c_float), ("sink", C.c_void_p), ("latent_v", C.c_int32), ("gate", C.c_void_p), ("gate_ld", C.c_int64), ("ctx_rows", C.c_int32), ("kd", C.c_int32), ("kv_ld", C.c_int64), ("krot", C.c_void_p), ("krot_ld", C.c_int64),
+                ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p), ("norm_full", C.c_int32), ("rot_half", C.c_int32), ("in_bias", C.c_void_p), ("kv_shared", C.c_int32),
+                ("vg", C.c_int32), ("softcap", C.c_float), ("head_scale", C.c_void_p), ("keep_first", C.c_int32), ("gate_elem", C.c_int32)]
 
 
 class RetentionDesc(C.Structure):
@@ -77,15 +81,24 @@ def retention_desc(H: int, D: int, V: int, decay: torch.Tensor, eps: float, k_sc
 
 
 def attn_desc(H: int, G: int, D: int, V: int, scale: float, *, values_from_keys: bool = False, gated: bool = True, chunk: int = 0, window: int = 0, pool: int = 0,
-              qk_eps: float = -1.0, rot_freq: Optional[torch.Tensor] = None, rot_scale: float = 1.0, sink: Optional[torch.Tensor] = None) -> "AttnDesc":
-    """descriptor for a projection row laid out q | k | v | gate (v absent when the values are the keys, gate absent when not gated);
-    rot_freq: device f32 [rot_dims / 2] (the caller keeps it alive)"""
+              qk_eps: float = -1.0, rot_freq: Optional[torch.Tensor] = None, rot_scale: float = 1.0, sink: Optional[torch.Tensor] = None,
+              q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None, norm_full: bool = False, rot_half: bool = False,
+              in_bias: Optional[torch.Tensor] = None, kv_shared: bool = False, value_heads: int = 0, softcap: float = 0.0, head_scale: Optional[torch.Tensor] = None,
+              keep_first: int = 0, gate_elem: bool = False) -> "AttnDesc":
+    """descriptor for a projection row laid out q | k | v | gate (v absent when the values are the keys, k and v absent when they are another
+    layer's (kv_shared), gate absent when not gated); value_heads: number of value heads when it is not G.
+    Device tensors (rot_freq f32 [rot_dims / 2], sink / head_scale f32 [H], norm weights, in_bias f32 [row width]) are kept alive by the caller."""
+    Gv = value_heads if value_heads > 0 else G
     k_col = H * D
     v_col = k_col if values_from_keys else k_col + G * D
-    end = v_col + (G * D if values_from_keys else G * V)
+    end = k_col if kv_shared else v_col + (G * D if values_from_keys else Gv * V)
+    ptr = lambda t: t.data_ptr() if t is not None else None
     d = AttnDesc(H, G, D, V, 0, k_col, v_col, end if gated else -1, scale, chunk, window, pool, qk_eps, 2 * rot_freq.numel() if rot_freq is not None else 0,
-                 rot_freq.data_ptr() if rot_freq is not None else None, rot_scale, sink.data_ptr() if sink is not None else None, 0)
-    d.width = end + (H if gated else 0)
+                 ptr(rot_freq), rot_scale, ptr(sink), 0)
+    d.q_norm_w, d.k_norm_w, d.norm_full, d.rot_half, d.in_bias = ptr(q_norm_w), ptr(k_norm_w), int(norm_full), int(rot_half), ptr(in_bias)
+    d.kv_shared, d.vg, d.softcap, d.head_scale, d.keep_first = int(kv_shared), (Gv if Gv != G else 0), softcap, ptr(head_scale), keep_first
+    d.gate_elem = int(gate_elem and gated)
+    d.width = end + ((H * V if gate_elem else H) if gated else 0)
     return d
 
 
@@ -306,8 +319,8 @@ def depth_norm(x_cur: torch.Tensor, out1: Optional[torch.Tensor], w1: Optional[t
 
 
 @_timed
-def attn_prep_ex(proj: torch.Tensor, step: "StepDesc", d: "AttnDesc", kpool: torch.Tensor, vpool: torch.Tensor, kpooled: Optional[torch.Tensor] = None,
-                 vpooled: Optional[torch.Tensor] = None):
+def attn_prep_ex(proj: torch.Tensor, step: "StepDesc", d: "AttnDesc", kpool: Optional[torch.Tensor], vpool: Optional[torch.Tensor],
+                 kpooled: Optional[torch.Tensor] = None, vpooled: Optional[torch.Tensor] = None):
     _, _, ld = _rows2d(proj)
     _check(lib().b200seq_attn_prep_ex(_p(proj), C.c_int64(ld), C.byref(step), C.byref(d), _p(kpool), _p(vpool), _p(kpooled), _p(vpooled), _st(proj)))
 
@@ -508,3 +521,102 @@ def argmax(logits: torch.Tensor, ids: torch.Tensor):
     R, V = logits.shape
     assert logits.is_contiguous() and ids.dtype == torch.int32
     _check(lib().b200seq_argmax(_p(logits), R, V, _p(ids), _st(logits)))
+
+
+# ---- layers with the norm on the sublayer's output, two-branch mixers, gated linear recurrences ----------------------------------------------
+ROUTE_SIGMOID, ROUTE_SOFTMAX = 0, 1
+
+
+@_timed
+def moe_route_ex(z: torch.Tensor, E: int, groups: int, keep: int, top: int, kind: int, correction: Optional[torch.Tensor], ids: torch.Tensor, wts: torch.Tensor,
+                 counts: Optional[torch.Tensor]):
+    """moe_route with the score kind (ROUTE_SIGMOID / ROUTE_SOFTMAX over the E logits) and a correction f32 [E] that enters the choice only"""
+    T, _, ldz = _rows2d(z)
+    assert ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.is_contiguous() and wts.is_contiguous() and ids.numel() >= T * top
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
+    _check(lib().b200seq_moe_route_ex(_p(z), C.c_int64(ldz), T, E, groups, keep, top, kind, _p(correction), _p(ids), _p(wts), _p(counts), _st(z)))
+
+
+@_timed
+def moe_combine_ex(ys: torch.Tensor, wts: torch.Tensor, slot_of: Optional[torch.Tensor], ids: torch.Tensor, E_real: int, x_id: torch.Tensor, T: int, top: int,
+                   shared: Optional[torch.Tensor], gate_z: Optional[torch.Tensor], y: torch.Tensor):
+    """moe_combine where a pair whose expert id is >= E_real is an identity expert: its output is the token's row of x_id (f32 [T, W])"""
+    W = y.shape[1]
+    assert ys.is_contiguous() and y.is_contiguous() and (shared is None or shared.is_contiguous()) and x_id.is_contiguous() and x_id.dtype == torch.float32
+    _check(lib().b200seq_moe_combine_ex(_p(ys), _p(wts), _p(slot_of), _p(ids), E_real, _p(x_id), T, top, W, _p(shared), _p(gate_z),
+                                        C.c_int64(gate_z.stride(0) if gate_z is not None else 0), _p(y), _st(y)))
+
+
+@_timed
+def causal_conv_ex(x: torch.Tensor, in_bias: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor], step: "StepDesc",
+                   mode: int, out: torch.Tensor, out2: Optional[torch.Tensor] = None):
+    """causal_conv over x + in_bias (mode 0: convolution + bias, nothing else); out2: a second copy of the result in its own type"""
+    T, Cn, ldx = _rows2d(x)
+    _, _, ldo = _rows2d(out)
+    ldo2 = _rows2d(out2)[2] if out2 is not None else 0
+    _check(lib().b200seq_causal_conv_ex(_p(x), C.c_int64(ldx), _p(in_bias), _p(w), _p(bias), _p(state), C.byref(step), Cn, w.shape[1], mode, _p(out), _DT[out.dtype],
+                                        C.c_int64(ldo), _p(out2), _DT[out2.dtype] if out2 is not None else F32, C.c_int64(ldo2), _st(x)))
+
+
+@_timed
+def embed_bigram(table: torch.Tensor, bigram: Optional[torch.Tensor], ids: torch.Tensor, ent_prev: torch.Tensor, step: "StepDesc", scale: float, buckets: int,
+                 mul_prev: int, mul_cur: int, x: torch.Tensor, a: Optional[torch.Tensor]):
+    """x[t] = table[ids[t]] * scale + bigram[hash(previous token, token)] (the last row of bigram at position 0); a: the same in its own type"""
+    W = x.shape[-1]
+    assert table.dtype == torch.bfloat16 and table.is_contiguous() and x.is_contiguous() and x.dtype == torch.float32 and (a is None or a.is_contiguous())
+    assert bigram is None or (bigram.dtype == torch.bfloat16 and bigram.is_contiguous() and tuple(bigram.shape) == (buckets + 1, W))
+    _check(lib().b200seq_embed_bigram(_p(table), _p(bigram), _p(ids), _p(ent_prev), C.byref(step), C.c_float(scale), buckets, mul_prev, mul_cur, W, _p(x), _p(a),
+                                      _DT[a.dtype] if a is not None else F32, _st(x)))
+
+
+@_timed
+def branch_norm(x: torch.Tensor, y1: torch.Tensor, w: torch.Tensor, eps: float, *, bias1: Optional[torch.Tensor] = None, w_b1: Optional[torch.Tensor] = None, s1: float = 1.0,
+                y2: Optional[torch.Tensor] = None, w_b2: Optional[torch.Tensor] = None, s2: float = 1.0, rows: Optional[torch.Tensor] = None,
+                x_out: Optional[torch.Tensor] = None, a_out: Optional[torch.Tensor] = None, fin_w: Optional[torch.Tensor] = None):
+    """x + rms_norm(s1 * b1 + s2 * b2) * w with b1 = y1 + bias1 (rms-normed with w_b1 when given), b2 = y2 (rms-normed with w_b2); see include/b200seq.h"""
+    W = x.shape[-1]
+    R = x.shape[0] if rows is None else rows.numel()
+    assert x.is_contiguous() and y1.is_contiguous() and (y2 is None or y2.is_contiguous()) and (a_out is None or a_out.is_contiguous())
+    _check(lib().b200seq_branch_norm(_p(x), _p(y1), _p(bias1), _p(w_b1), C.c_float(s1), _p(y2), _p(w_b2), C.c_float(s2), _p(w), C.c_float(eps), W, _p(rows), R, _p(x_out),
+                                     _p(a_out), _DT[a_out.dtype] if a_out is not None else F32, _p(fin_w), _st(x)))
+
+
+@_timed
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor):
+    """out = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 per row, N = division by the root mean square; coef device f32 [4]"""
+    T, F, ldz = _rows2d(z)
+    _, _, ldo = _rows2d(out)
+    assert coef.dtype == torch.float32 and coef.numel() == 4 and out.shape[1] == F
+    _check(lib().b200seq_polynorm(_p(z), C.c_int64(ldz), T, F, _p(coef), C.c_float(eps), _p(out), _DT[out.dtype], C.c_int64(ldo), _st(z)))
+
+
+@_timed
+def softcap(x: torch.Tensor, cap: float):
+    assert x.is_contiguous() and x.dtype == torch.float32
+    _check(lib().b200seq_softcap(_p(x), C.c_int64(x.numel()), C.c_float(cap), _st(x)))
+
+
+@_timed
+def diff_combine(a: torch.Tensor, H: int, G: int, V: int, lam: float, out_scale: float, eps: float, out: torch.Tensor):
+    """a f32 [T, 2 * H * V], the two maps per head in the order [key group][map][head of the group] -> out [T, H * V] = unit_rms(a1 - lam * a2) * out_scale"""
+    T = a.shape[0]
+    assert a.is_contiguous() and a.dtype == torch.float32 and a.shape[1] == 2 * H * V and out.is_contiguous() and tuple(out.shape) == (T, H * V)
+    _check(lib().b200seq_diff_combine(_p(a), T, H, G, V, C.c_float(lam), C.c_float(out_scale), C.c_float(eps), _p(out), _DT[out.dtype], _st(a)))
+
+
+@_timed
+def min_gru(proj: torch.Tensor, z_col: int, x_col: int, g_col: int, bias: Optional[torch.Tensor], state: torch.Tensor, step: "StepDesc", Cn: int, out: torch.Tensor):
+    _, _, ldp = _rows2d(proj)
+    assert out.is_contiguous() and out.shape[1] == Cn and state.is_contiguous() and state.shape[1] == Cn
+    _check(lib().b200seq_min_gru(_p(proj), C.c_int64(ldp), z_col, x_col, g_col, _p(bias), _p(state), C.byref(step), Cn, _p(out), _DT[out.dtype], _st(proj)))
+
+
+@_timed
+def rg_lru(u: torch.Tensor, gates: torch.Tensor, gate_bias: Optional[torch.Tensor], sp_lam: torch.Tensor, decay_c: float, proj: torch.Tensor, y_col: int,
+           bias: Optional[torch.Tensor], state: torch.Tensor, step: "StepDesc", blocks: int, out: torch.Tensor):
+    _, Cn, ldu = _rows2d(u)
+    _, _, ldg = _rows2d(gates)
+    _, _, ldp = _rows2d(proj)
+    assert out.is_contiguous() and out.shape[1] == Cn and state.is_contiguous() and state.shape[1] == Cn and sp_lam.numel() == Cn
+    _check(lib().b200seq_rg_lru(_p(u), C.c_int64(ldu), _p(gates), C.c_int64(ldg), _p(gate_bias), _p(sp_lam), C.c_float(decay_c), _p(proj), C.c_int64(ldp), y_col, _p(bias),
+                                _p(state), C.byref(step), Cn, blocks, _p(out), _DT[out.dtype], _st(proj)))

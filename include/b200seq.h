@@ -195,6 +195,18 @@ typedef struct b200seq_attn_desc {
     int64_t kv_ld;      /* attend: > 0: floats per position row of kpool and of vpool (default G * D and G * V) */
     const float* krot;
     int64_t krot_ld;
+    /* ---- fields below default to zero / null (older initialisers leave them so) ---- */
+    const float* q_norm_w; /* prep: weighted RMS norm of q (needs qk_eps >= 0): [D] shared by all heads, or [H * D] when norm_full */
+    const float* k_norm_w; /* prep: the same for k: [D] or [G * D] */
+    int32_t norm_full;     /* prep: 1 = the RMS is taken over the whole q projection (all heads at once), and over the whole k projection */
+    int32_t rot_half;      /* prep: 1 = rotated pairs are (i, i + rot_dims / 2) instead of (2i, 2i + 1) */
+    const float* in_bias;  /* prep: f32 bias of the projection row (indexed by the row's columns), added to q, k and v before everything else */
+    int32_t kv_shared;     /* prep: 1 = keys and values of this layer are another layer's pool rows: only the queries are prepared */
+    int32_t vg;            /* > 0: number of value heads when it differs from G (G % vg == 0): key head g reads value head g / (G / vg) */
+    float softcap;         /* attend: > 0: score <- softcap * tanh(score / softcap) after scaling */
+    const float* head_scale; /* attend: device f32 [H] or null: the score of head h is also multiplied by head_scale[h] */
+    int32_t keep_first;    /* attend (window > 0): positions j < keep_first stay visible to every later position, at their true positions */
+    int32_t gate_elem;     /* attend (gate_col >= 0): 1 = one gate logit per output element, H * V of them at gate_col (or in `gate`), instead of one per head */
 } b200seq_attn_desc;
 int b200seq_attn_prep_ex(float* proj, int64_t ld, const b200seq_step* st, const b200seq_attn_desc* d, float* kpool, float* vpool, float* kpooled, float* vpooled,
                          void* stream);
@@ -302,6 +314,61 @@ int b200seq_moe_gather(const void* x_bf16, int64_t ldx, const int32_t* sorted, i
  * gate_z null with shared: the shared branch is added as it is.  ys, shared, y: f32 [., W]. */
 int b200seq_moe_combine(const float* ys, const float* wts, const int32_t* slot_of, int T, int top, int W, const float* shared, const float* gate_z, int64_t ldg,
                         float* y, void* stream);
+
+/* ---- the same choice with soft-max scores and a correction -------------------------------------------------------------------------------
+ * kind 0: s = sigmoid(z) (b200seq_moe_route); kind 1: s = softmax(z[0 .. E)) in f32.  correction (f32 [E] or null) is added to s for the
+ * CHOICE only; the weights are the chosen s / (their sum + 1e-20).  E counts every router output, identity experts included. */
+int b200seq_moe_route_ex(const float* z, int64_t ldz, int T, int E, int groups, int keep, int top, int kind, const float* correction, int32_t* ids, float* wts,
+                         int32_t* counts, void* stream);
+/* b200seq_moe_combine with identity experts: a pair whose expert id is >= E_real has no row in ys; its output is the token's own input
+ * x_id[t] (f32 [T, W]) times the weight.  ids: [T * top]. */
+int b200seq_moe_combine_ex(const float* ys, const float* wts, const int32_t* slot_of, const int32_t* ids, int E_real, const float* x_id, int T, int top, int W,
+                           const float* shared, const float* gate_z, int64_t ldg, float* y, void* stream);
+
+/* ---- b200seq_causal_conv with a bias on the INPUT (the convolution sees x + in_bias, zeros before the sequence's start; the carried state
+ * holds the biased inputs) and an optional second copy of the result in out2_dtype (row stride ldo2). */
+int b200seq_causal_conv_ex(const float* x, int64_t ldx, const float* in_bias, const float* w, const float* bias, float* state, const b200seq_step* st, int C, int taps,
+                           int mode, void* out, int out_dtype, int64_t ldo, void* out2, int out2_dtype, int64_t ldo2, void* stream);
+
+/* ---- embedding with a hashed bigram table ---------------------------------------------------------------------------------------------------
+ * x[t] = table[ids[t]] * scale + bigram[row], row = (prev * mul_prev + ids[t] * mul_cur) mod buckets with prev the sequence's previous token:
+ * ids[t - 1] inside a portion, ent_prev[e] for a portion's first token, and row = buckets (the table's last row) at position 0.
+ * table bf16 [vocab, W]; bigram bf16 [buckets + 1, W] or null; ent_prev int32 [B].  x f32 [T, W]; a (optional) the same in a_dtype. */
+int b200seq_embed_bigram(const void* table_bf16, const void* bigram_bf16, const int32_t* ids, const int32_t* ent_prev, const b200seq_step* st, float scale,
+                         int buckets, int mul_prev, int mul_cur, int W, float* x, void* a, int a_dtype, void* stream);
+
+/* ---- residual path with the norm on the sublayer's OUTPUT -----------------------------------------------------------------------------------
+ * One block per row r (token t = rows ? rows[r] : r).  A sublayer's result is one branch y1 or the sum of two:
+ *   b1 = y1[t] + bias1 (bias1 optional);  if w_b1: b1 <- rms_norm(b1, eps) * w_b1;   likewise b2 from y2 with w_b2 (y2 optional, no bias)
+ *   v = s1 * b1 + s2 * b2;   x_new = x[t] + rms_norm(v, eps) * w
+ *   x_out[t] <- x_new (optional, may be x);   a_out[r] <- fin_w ? rms_norm(x_new, eps) * fin_w : x_new, in out_dtype (optional)
+ * rms_norm(u) = u / sqrt(mean(u^2) + eps).  Everything in f32. */
+int b200seq_branch_norm(const float* x, const float* y1, const float* bias1, const float* w_b1, float s1, const float* y2, const float* w_b2, float s2,
+                        const float* w, float eps, int W, const int32_t* rows, int R, float* x_out, void* a_out, int out_dtype, const float* fin_w, void* stream);
+
+/* out[t] = c0 * N(z) + c1 * N(z^2) + c2 * N(z^3) + c3 with powers taken element by element and N(u) = u / sqrt(mean(u^2) + eps) over the
+ * F values of the row; z f32 [T, F] (stride ldz), coef device f32 [4], out [T, F] in out_dtype (stride ldo). */
+int b200seq_polynorm(const float* z, int64_t ldz, int T, int F, const float* coef, float eps, void* out, int out_dtype, int64_t ldo, void* stream);
+
+/* x <- cap * tanh(x / cap) on n floats, in place */
+int b200seq_softcap(float* x, int64_t n, float cap, void* stream);
+
+/* Differential attention, second half: a f32 [T, 2 * H * V] holds the two maps' results per head in the order [g][map][r] (g < G key groups,
+ * r < H / G heads of a group); out[t][h] = rms_norm(a1 - lambda * a2, eps) * out_scale over the V values of head h = g * (H / G) + r,
+ * written in out_dtype as [T, H * V]. */
+int b200seq_diff_combine(const float* a, int T, int H, int G, int V, float lambda, float out_scale, float eps, void* out, int out_dtype, void* stream);
+
+/* ---- element-wise gated linear recurrences S_t = a_t * S_(t-1) + b_t with per-slot f32 state [slots][C] (zero when ent_pos0 == 0) -----------
+ * min_gru:  z = sigmoid(proj[z_col + c] + bias[z_col + c]), u = proj[x_col + c] + bias[x_col + c], cand = u >= 0 ? u + 0.5 : sigmoid(u);
+ *           a = 1 - z, b = z * cand;   out[t][c] = S_t * silu(proj[g_col + c])          (bias: f32 indexed by the projection row's columns, or null)
+ * rg_lru:   r = sigmoid(gates[blk][c'] + gate_bias[..]), i = sigmoid(gates[blk][bw + c'] + ..) with gates rows laid out per block of bw = C / blocks
+ *           channels as [r (bw) | i (bw)] and gate_bias the same layout; log a = -decay_c * r * sp_lam[c] (sp_lam = softplus(lam), precomputed),
+ *           a = exp(log a), b = sqrt(1 - a^2) * i * u[t][c];   out[t][c] = S_t * gelu_tanh(proj[y_col + c] + bias[y_col + c])
+ * proj, u, gates: f32 rows; out [T, C] in out_dtype. */
+int b200seq_min_gru(const float* proj, int64_t ldp, int z_col, int x_col, int g_col, const float* bias, float* state, const b200seq_step* st, int C, void* out,
+                    int out_dtype, void* stream);
+int b200seq_rg_lru(const float* u, int64_t ldu, const float* gates, int64_t ldg, const float* gate_bias, const float* sp_lam, float decay_c, const float* proj,
+                   int64_t ldp, int y_col, const float* bias, float* state, const b200seq_step* st, int C, int blocks, void* out, int out_dtype, void* stream);
 
 /* ids[r] = argmax_v logits[r][v] (first maximum) */
 int b200seq_argmax(const float* logits, int R, int V, int32_t* ids, void* stream);
