@@ -307,7 +307,8 @@ def test_constants_are_read_from_the_configuration(cases):
     assert changed(lambda w: w["layers"][1]["mlp"]["router"].update(top=1)) > 20 * TOL32
     assert changed(lambda w: w["norm"].update(eps=1e-3)) > 20 * TOL32
     for name in ("l1.mix.left.sink", "l1.mix.left.temp", "l1.mlp.correction", "l1.mix.left.o.b", "l1.mix.right.z.b", "l2.mix.right.conv.b", "l2.mix.right.ri.b", "l0.mix.q.b"):
-        other = {k: (v + 0.25 if k == name else v) for k, v in c.P.items()}
+        # (a shift of all corrections alike would leave every choice as it was)
+        other = {k: ((-3.0 * v if name.endswith("correction") else v + 0.25) if k == name else v) for k, v in c.P.items()}
         assert changed(lambda w: None, other) > 20 * TOL32, name
 
 
