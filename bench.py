@@ -42,7 +42,7 @@ def parse_args():
     ap.add_argument("--prompt", type=int, default=32, help="prompt tokens fed before the timed region (reference bench.rs:24)")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements (prefill GEMM, batch-32)")
     ap.add_argument("--layered", default=None, metavar="DESIGN", help="instead of the default workload: prefill / decode throughput and the per-kernel "
-                    "roofline table of a layer-list design (fenorax, gemosun, teselix) at real-model layer sizes, beside the dense decoder of equal size (1 GPU)")
+                    "roofline table of a layer-list design (fenorax, gemosun, teselix, pafelorn) at real-model layer sizes, beside the dense decoder of equal size (1 GPU)")
     ap.add_argument("--layered-sizes", default="w1024,w2048,w4096", help="comma list of blazr_b200.layered_bench.SIZES keys")
     ap.add_argument("--layered-prompt", type=int, default=4096)
     ap.add_argument("--layered-context", type=int, default=1024)

@@ -142,8 +142,13 @@ __global__ void diff_combine_kernel(const float* __restrict__ a, int H, int G, i
 }
 
 // ---- gated linear recurrences ------------------------------------------------------------------------------------------------------------------
-// One thread per (entry, channel) walks the entry's tokens in order; neighbouring threads hold neighbouring channels, so every load and
-// store of a time step is coalesced, and the loads of a step do not depend on the recurrence (the compiler keeps several steps in flight).
+// S_t = a_t S_(t-1) + b_t per channel, out_t = S_t * o_t; (a_t, b_t, o_t) depend on the token's own inputs only.
+// Two forms with the same result up to rounding:
+//   steps of single tokens: one thread per (entry, channel) (neighbouring threads = neighbouring channels: coalesced);
+//   steps with portions:    a block = 32 channels x 16 warps; warp w takes tokens [w * 32, w * 32 + 32) of every group of 512 tokens, keeps
+//                           their (a, b, o) in registers and reduces them to (A, B) = (product of a, local end state from 0); the warps' (A, B) are
+//                           chained through shared memory to every warp's entry state, and the tokens are replayed from the registers.
+//                           Every input is read once and every output written once.
 struct GruArgs {
     const float* proj;
     int64_t ldp;
@@ -154,27 +159,19 @@ struct GruArgs {
     void* out;
     int out_dtype;
 };
-__global__ void min_gru_kernel(const GruArgs a, const b200seq_step st) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    const int e = blockIdx.y;
-    if (c >= a.C) return;
-    const int t0 = st.ent_start[e], t1 = st.ent_start[e + 1];
-    if (t1 <= t0) return;
-    float* sp = a.state + (int64_t)st.ent_slot[e] * a.C + c;
-    float S = st.ent_pos0[e] == 0 ? 0.f : *sp;
-    const float bz = a.bias ? a.bias[a.z_col + c] : 0.f, bx = a.bias ? a.bias[a.x_col + c] : 0.f;
-#pragma unroll 4
-    for (int t = t0; t < t1; ++t) {
+struct GruCoef {
+    float bz, bx;
+    __device__ __forceinline__ void init(const GruArgs& a, int c) {
+        bz = a.bias ? a.bias[a.z_col + c] : 0.f, bx = a.bias ? a.bias[a.x_col + c] : 0.f;
+    }
+    __device__ __forceinline__ void at(const GruArgs& a, int t, int c, float& av, float& bv, float& ov) const {
         const float* p = a.proj + (int64_t)t * a.ldp;
         const float z = sigmoidf_acc(p[a.z_col + c] + bz);
         const float u = p[a.x_col + c] + bx;
-        const float g = p[a.g_col + c];
         const float cand = u >= 0.f ? u + 0.5f : sigmoidf_acc(u);
-        S = fmaf(z, cand - S, S);   // (1 - z) S + z cand
-        store_act(a.out, a.out_dtype, (int64_t)t * a.C + c, S * siluf_acc(g));
+        av = 1.f - z, bv = z * cand, ov = siluf_acc(p[a.g_col + c]);
     }
-    *sp = S;
-}
+};
 
 struct LruArgs {
     const float* u;
@@ -192,7 +189,28 @@ struct LruArgs {
     void* out;
     int out_dtype;
 };
-__global__ void rg_lru_kernel(const LruArgs a, const b200seq_step st) {
+struct LruCoef {
+    int rc, ic;
+    float br, bi, by, k;
+    __device__ __forceinline__ void init(const LruArgs& a, int c) {
+        const int blk = c / a.bw, cc = c - blk * a.bw;
+        rc = blk * 2 * a.bw + cc, ic = rc + a.bw;
+        br = a.gate_bias ? a.gate_bias[rc] : 0.f, bi = a.gate_bias ? a.gate_bias[ic] : 0.f;
+        by = a.bias ? a.bias[a.y_col + c] : 0.f;
+        k = -a.decay_c * a.sp_lam[c];
+    }
+    __device__ __forceinline__ void at(const LruArgs& a, int t, int c, float& av, float& bv, float& ov) const {
+        const float* gp = a.gates + (int64_t)t * a.ldg;
+        const float r = sigmoidf_acc(gp[rc] + br), ig = sigmoidf_acc(gp[ic] + bi);
+        const float la = k * r;
+        av = expf(la);
+        bv = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * ig * a.u[(int64_t)t * a.ldu + c];   // sqrt(1 - a^2) without cancellation near a = 1
+        ov = gelu_tanhf_acc(a.proj[(int64_t)t * a.ldp + a.y_col + c] + by);
+    }
+};
+
+template <typename Args, typename Coef>
+__global__ void scan_step_kernel(const Args a, const b200seq_step st) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int e = blockIdx.y;
     if (c >= a.C) return;
@@ -200,24 +218,70 @@ __global__ void rg_lru_kernel(const LruArgs a, const b200seq_step st) {
     if (t1 <= t0) return;
     float* sp = a.state + (int64_t)st.ent_slot[e] * a.C + c;
     float S = st.ent_pos0[e] == 0 ? 0.f : *sp;
-    const int blk = c / a.bw, cc = c - blk * a.bw;
-    const int rc = blk * 2 * a.bw + cc, ic = rc + a.bw;
-    const float br = a.gate_bias ? a.gate_bias[rc] : 0.f, bi = a.gate_bias ? a.gate_bias[ic] : 0.f;
-    const float by = a.bias ? a.bias[a.y_col + c] : 0.f;
-    const float k = -a.decay_c * a.sp_lam[c];
+    Coef k;
+    k.init(a, c);
 #pragma unroll 4
     for (int t = t0; t < t1; ++t) {
-        const float* gp = a.gates + (int64_t)t * a.ldg;
-        const float r = sigmoidf_acc(gp[rc] + br), ig = sigmoidf_acc(gp[ic] + bi);
-        const float la = k * r;
-        const float av = expf(la);
-        const float mult = sqrtf(fmaxf(-expm1f(2.f * la), 0.f));   // sqrt(1 - a^2) without cancellation near a = 1
-        const float uv = a.u[(int64_t)t * a.ldu + c];
-        S = fmaf(av, S, mult * ig * uv);
-        const float y = gelu_tanhf_acc(a.proj[(int64_t)t * a.ldp + a.y_col + c] + by);
-        store_act(a.out, a.out_dtype, (int64_t)t * a.C + c, S * y);
+        float av, bv, ov;
+        k.at(a, t, c, av, bv, ov);
+        S = fmaf(av, S, bv);
+        store_act(a.out, a.out_dtype, (int64_t)t * a.C + c, S * ov);
     }
     *sp = S;
+}
+
+constexpr int SC_L = 32, SC_NW = 16;
+template <typename Args, typename Coef>
+__global__ void __launch_bounds__(SC_NW * 32, 1) scan_chunk_kernel(const Args a, const b200seq_step st) {
+    __shared__ float sA[SC_NW][32], sB[SC_NW][32];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;
+    const int e = blockIdx.y;
+    const bool valid = c < a.C;
+    const int cc = valid ? c : a.C - 1;
+    const int t0 = st.ent_start[e], t1 = st.ent_start[e + 1];
+    if (t1 <= t0) return;
+    float* sp = a.state + (int64_t)st.ent_slot[e] * a.C + cc;
+    float S = st.ent_pos0[e] == 0 ? 0.f : *sp;
+    Coef k;
+    k.init(a, cc);
+    for (int g0 = t0; g0 < t1; g0 += SC_NW * SC_L) {
+        const int base = g0 + wid * SC_L;
+        float av[SC_L], bv[SC_L], ov[SC_L];
+        float A = 1.f, B = 0.f;
+#pragma unroll
+        for (int i = 0; i < SC_L; ++i) {
+            av[i] = 1.f, bv[i] = 0.f, ov[i] = 0.f;
+            if (base + i < t1) k.at(a, base + i, cc, av[i], bv[i], ov[i]);
+            B = fmaf(av[i], B, bv[i]);
+            A *= av[i];
+        }
+        sA[wid][lane] = A, sB[wid][lane] = B;
+        __syncthreads();
+        float s = S;
+        for (int w = 0; w < wid; ++w) s = fmaf(sA[w][lane], s, sB[w][lane]);
+        float send = s;
+        for (int w = wid; w < SC_NW; ++w) send = fmaf(sA[w][lane], send, sB[w][lane]);
+#pragma unroll
+        for (int i = 0; i < SC_L; ++i) {
+            s = fmaf(av[i], s, bv[i]);
+            if (base + i < t1 && valid) store_act(a.out, a.out_dtype, (int64_t)(base + i) * a.C + c, s * ov[i]);
+        }
+        S = send;
+        __syncthreads();   // sA / sB are rewritten by the next group
+    }
+    if (wid == 0 && valid) *sp = S;
+}
+
+template <typename Args, typename Coef>
+static int launch_scan(const Args& a, const b200seq_step* st, cudaStream_t cs) {
+    if (st->T == st->B) {   // one token per entry
+        const int nt = a.C >= 4096 ? 128 : (a.C >= 1024 ? 64 : 32);
+        scan_step_kernel<Args, Coef><<<dim3((a.C + nt - 1) / nt, st->B), nt, 0, cs>>>(a, *st);
+    } else {
+        scan_chunk_kernel<Args, Coef><<<dim3((a.C + 31) / 32, st->B), SC_NW * 32, 0, cs>>>(a, *st);
+    }
+    return 0;
 }
 
 }  // namespace b200seq
@@ -287,8 +351,7 @@ int b200seq_min_gru(const float* proj, int64_t ldp, int z_col, int x_col, int g_
     if (st->T == 0 || st->B == 0) return 0;
     if (st->B > 65535) return fail(B200SEQ_ERR_UNSUPPORTED, "min_gru: too many entries");
     const GruArgs a{proj, ldp, z_col, x_col, g_col, bias, state, C, out, out_dtype};
-    const int nt = C >= 4096 ? 128 : (C >= 1024 ? 64 : 32);
-    min_gru_kernel<<<dim3((C + nt - 1) / nt, st->B), nt, 0, (cudaStream_t)stream>>>(a, *st);
+    launch_scan<GruArgs, GruCoef>(a, st, (cudaStream_t)stream);
     SEQ_LAUNCH_CHECK("min_gru");
     return 0;
 }
@@ -300,8 +363,7 @@ int b200seq_rg_lru(const float* u, int64_t ldu, const float* gates, int64_t ldg,
     if (st->T == 0 || st->B == 0) return 0;
     if (st->B > 65535) return fail(B200SEQ_ERR_UNSUPPORTED, "rg_lru: too many entries");
     const LruArgs a{u, ldu, gates, ldg, gate_bias, sp_lam, decay_c, proj, ldp, y_col, bias, state, C, C / blocks, out, out_dtype};
-    const int nt = C >= 4096 ? 128 : (C >= 1024 ? 64 : 32);
-    rg_lru_kernel<<<dim3((C + nt - 1) / nt, st->B), nt, 0, (cudaStream_t)stream>>>(a, *st);
+    launch_scan<LruArgs, LruCoef>(a, st, (cudaStream_t)stream);
     SEQ_LAUNCH_CHECK("rg_lru");
     return 0;
 }

@@ -6,10 +6,12 @@ dense-attention decoder (blazr_b200/decode.py, Q8_0 weights) of the same width, 
     kernels  : every operator of one prefill step and one decode step timed alone (CUDA events around each launch), with its
                algorithmic bytes / FLOPs and the fraction of the roofline it reaches; the like kernels of the decoder beside them
 
-`python bench.py --layered fenorax|gemosun|teselix [--layered-sizes w1024,w2048]` prints the result as one JSON line; bench.py's default
+`python bench.py --layered fenorax|gemosun|teselix|pafelorn [--layered-sizes w1024,w2048]` prints the result as one JSON line; bench.py's default
 workload and JSON line are untouched.  For Gemosun (parallel attention / feed-forward layers, three of four feed-forwards a mixture of
 experts) the closest existing model, Fenorax at the same sizes, runs beside it as well; for Teselix (retention and latent-attention mixers,
-table-routed experts) both run beside it: Gemosun is the closest in attention and experts, Fenorax in the recurrence.
+table-routed experts) both run beside it: Gemosun is the closest in attention and experts, Fenorax in the recurrence.  For Pafelorn (windowed
+attention beside element-wise recurrences, differential attention, soft-max-routed gated experts) Gemosun (windowed attention with rotation,
+routed experts) and Fenorax (a recurrence with carried state and a short convolution) run beside it as well.
 """
 from __future__ import annotations
 
@@ -70,6 +72,90 @@ def teselix_config(sz: dict, experts: int = 32, top: int = 4, kv_rank: int = 256
            "mixer": {"heads": H, "dim": D, "rot_dim": D // 2, "vdim": D, "q_rank": 3 * W // 8, "kv_rank": kv_rank, "scale": (D + D // 2) ** -0.5,
                      "rot": {"dims": D // 2, "base": 10000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
     return {"architecture": "Teselix", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "postln_alpha": 2.0, "layers": [ret, lat, dict(ret), dict(lat)]}
+
+
+def pafelorn_config(sz: dict, experts: int = 32, identity: int = 4, top: int = 4) -> dict:
+    """four out-norm layers [differential attention + dense, attention | minGRU + experts, attention | gated LRU + dense, differential attention over
+    layer 0's keys and values + experts] of the size's width and head layout; windows of `chunk` positions; differential heads are half as many with
+    values twice as wide; both recurrences are as wide as the model; an expert is a quarter of the dense size"""
+    H, G, D, W = sz["heads"], sz["kv_heads"], sz["dim"], sz["width"]
+    eff = sz["ff"] // 4
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": experts, "identity": identity, "top": top}, "shared": {"ff": eff, "limit": 7.0}}
+    dense = {"kind": "dense", "ff": sz["ff"]}
+    diff = {"heads": H // 2, "kv_heads": max(G // 2, 1), "dim": D, "vdim": 2 * D, "scale": D ** -0.5, "diff": 0.5, "mask": {"size": sz["chunk"]},
+            "rot": {"dims": D, "base": 250000.0, "scaling": {"factor": 8.0}}}
+    left1 = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": sz["chunk"]},
+             "rot": {"dims": D // 2, "base": 250000.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    left2 = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 30.0, "mask": {"size": sz["chunk"], "keep_first": 4},
+             "rot": {"dims": D // 2, "base": 10000.0, "scaling": {"factor": 2.0}}}
+    return {"architecture": "Pafelorn", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "embedding": {"scale": float(W) ** 0.5, "bigram": {"buckets": 16381, "mul_prev": 31, "mul_cur": 17}},
+            "layers": [{"type": "attention", "mixer": diff, "mlp": dense},
+                       {"type": "parallel", "mixer": {"left": left1, "right": {"width": W}, "left_scale": 0.8, "right_scale": 0.9}, "mlp": moe},
+                       {"type": "parallel_2", "mixer": {"left": left2, "right": {"width": W, "blocks": 8, "conv": 4}}, "mlp": dict(dense)},
+                       {"type": "attention", "mixer": dict(diff, kv_from=0), "mlp": dict(moe)}]}
+
+
+def random_tensors_pafelorn(cfg: dict, device, seed: int = 7):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(shape, generator=g, device=device) * scale).to(torch.bfloat16)
+
+    ones = lambda *n: torch.ones(*n, dtype=torch.bfloat16, device=device)
+    zeros = lambda *n: torch.zeros(*n, dtype=torch.bfloat16, device=device)
+    t = {"embed": rnd(V, W, scale=W ** -0.5), "bigram": rnd(cfg["embedding"]["bigram"]["buckets"] + 1, W), "head": rnd(V, W, scale=W ** -0.5), "final.norm": ones(W)}
+
+    def lin(name, o, i, bias=False):
+        t[name] = rnd(o, i, scale=i ** -0.5)
+        if bias:
+            t[name + ".b"] = rnd(o, scale=0.1)
+
+    for i, lay in enumerate(cfg["layers"]):
+        p, m, mlp = f"l{i}.", lay["mixer"], lay["mlp"]
+        t[p + "norm1"], t[p + "norm2"] = ones(W), ones(W)
+        kind = lay["type"]
+        a, ap = (m, p + "mix.") if kind == "attention" else (m["left"], p + "mix.left.")
+        H, G, D, Vd = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+        maps = 2 if kind == "attention" else 1
+        b = kind != "parallel_2"
+        lin(ap + "q", H * maps * D, W, b)
+        if a.get("kv_from") is None:
+            lin(ap + "k", G * maps * D, W, b)
+            lin(ap + "v", G * Vd, W, b)
+            t[ap + "k.norm"] = ones(G * D) if kind == "parallel_2" else ones(D)
+        t[ap + "q.norm"] = ones(H * D) if kind == "parallel_2" else ones(D)
+        lin(ap + "o", W, H * Vd, kind == "parallel")
+        if kind == "attention":
+            for nm in ("lq1", "lk1", "lq2", "lk2"):
+                t[ap + nm] = rnd(D, scale=0.1)
+        elif kind == "parallel":
+            t[ap + "temp"], t[ap + "sink"] = ones(H), zeros(H)
+            r, C = p + "mix.right.", m["right"]["width"]
+            lin(r + "z", C, W, True), lin(r + "x", C, W, True), lin(r + "g", C, W), lin(r + "o", W, C)
+        else:
+            lin(ap + "g", H * Vd, W)
+            r, C, nb, taps = p + "mix.right.", m["right"]["width"], m["right"]["blocks"], m["right"]["conv"]
+            lin(r + "y", C, W, True), lin(r + "x", C, W, True), lin(r + "o", W, C)
+            t[r + "conv"], t[r + "conv.b"] = rnd(C, taps, scale=0.5), zeros(C)
+            for nm in ("ra", "ri"):
+                t[r + nm], t[r + nm + ".b"] = rnd(nb, C // nb, C // nb, scale=(C // nb) ** -0.5), zeros(nb, C // nb)
+            t[r + "lam"] = rnd(C) - 2.0
+            t[p + "mix.left.out"], t[p + "mix.right.out"] = ones(W), ones(W)
+        if mlp["kind"] == "dense":
+            lin(p + "mlp.up", mlp["ff"], W), lin(p + "mlp.down", W, mlp["ff"])
+            t[p + "mlp.act"] = torch.tensor([0.5, 0.3, 0.2, 0.0], device=device).to(torch.bfloat16)
+        else:
+            rt = mlp["router"]
+            lin(p + "mlp.router", rt["experts"] + rt["identity"], W)
+            t[p + "mlp.correction"] = zeros(rt["experts"] + rt["identity"])
+            for e in range(rt["experts"]):
+                lin(p + f"mlp.e{e}.gate", mlp["expert"]["ff"], W), lin(p + f"mlp.e{e}.up", mlp["expert"]["ff"], W), lin(p + f"mlp.e{e}.down", W, mlp["expert"]["ff"])
+            lin(p + "mlp.shared.gate", mlp["shared"]["ff"], W), lin(p + "mlp.shared.up", mlp["shared"]["ff"], W), lin(p + "mlp.shared.down", W, mlp["shared"]["ff"])
+            lin(p + "mlp.shared.sg", 1, W)
+    return lambda name: t[name].cpu()
 
 
 def random_tensors_teselix(cfg: dict, device, seed: int = 7):
@@ -185,7 +271,7 @@ def _events():
 
 def _linear_weights(model: LayeredModel) -> int:
     """weights of the linear layers a token goes through (of a mixture of experts: the router, the chosen experts, the shared one)"""
-    n = sum(L[k].numel() for L in model.layers for k in ("w_in", "w_o", "w_gu", "w_down", "w_router", "w_sup", "w_sdown", "rg1", "rg2", "w_uq", "w_ukT", "w_uv") if k in L)
+    n = sum(L[k].numel() for L in model.layers for k in ("w_in", "w_o", "w_gu", "w_down", "w_router", "w_sup", "w_sdown", "rg1", "rg2", "w_uq", "w_ukT", "w_uv", "w_up", "w_ro", "w_gates") if k in L)
     for L in model.layers:
         if "w_eup" in L:
             n += L["spec"].ff.top * (L["w_eup"][0].numel() + L["w_edown"][0].numel())
@@ -261,6 +347,24 @@ def _cost(name: str, shapes, scal, scen: dict, kw: dict = None):
         keys = scen["visible_keys"]                              # sum over the step's tokens of the keys each one sees
         kv_once = scen["kv_rows_touched"] * G * (D if getattr(d, "latent_v", 0) else D + V) * 4 if name == "attn_ex" else scen["kv_rows_touched"] * G * (D + V) * 4   # every visible K / V row once
         return kv_once + T * H * (D + V) * 4, 2.0 * keys * H * (D + V), "f32" if scen["prefill"] else "hbm"
+    if name == "min_gru":         # three f32 columns of the projection row per channel in, the gated state out; the entries' states read and written
+        T, C, oe = sh[0][0][0], scal[3], sh[-1][1]
+        return T * C * (12 + oe) + 2 * scen["entries"] * C * 4, 12.0 * T * C, "hbm"
+    if name == "rg_lru":          # u, two gate columns and the y column in, the gated state out
+        (T, C), oe = sh[0][0], sh[-1][1]
+        return T * C * (16 + oe) + 2 * scen["entries"] * C * 4, 16.0 * T * C, "hbm"
+    if name == "causal_conv_ex":  # the input column in, the result out in f32 and in the activation type
+        (T, C) = sh[0][0]
+        return T * C * sum(s[1] for s in sh if s[0] == (T, C)), 0.0, "hbm"
+    if name == "branch_norm":     # x and the branches in; x and / or the activation rows out
+        rows = kw["rows"][0][0] if isinstance(kw.get("rows"), tuple) else sh[0][0][0]
+        W = sh[0][0][1]
+        reads = 2 + (1 if isinstance(kw.get("y2"), tuple) else 0)
+        outs = sum(kw[n][1] for n in ("x_out", "a_out") if isinstance(kw.get(n), tuple))
+        return rows * W * (4 * reads + outs), 0.0, "hbm"
+    if name == "embed_bigram":    # two bf16 table rows in, the residual and the activation rows out
+        (T, W) = sh[-2][0] if len(sh) >= 2 else sh[-1][0]
+        return T * W * (4 + 4 + sh[-1][1]), 0.0, "hbm"
     if name == "ssm_scan":
         T, (H, V, N, G) = sh[0][0][0], scal[2:6]
         B = scen["entries"]
@@ -329,9 +433,12 @@ def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, ba
     elif design.lower() == "teselix":
         cfg = teselix_config(sz)
         model = LayeredModel(registry.LAYERED["Teselix"](cfg), random_tensors_teselix(cfg, dev), dev, dtype)
+    elif design.lower() == "pafelorn":
+        cfg = pafelorn_config(sz)
+        model = LayeredModel(registry.LAYERED["Pafelorn"](cfg), random_tensors_pafelorn(cfg, dev), dev, dtype)
     else:
         raise ValueError(f"no synthetic workload for design '{design}'")
-    gem, tes = design.lower() == "gemosun", design.lower() == "teselix"
+    gem, tes, paf = design.lower() == "gemosun", design.lower() == "teselix", design.lower() == "pafelorn"
     pool = 16 if gem else 0
     desc0 = next((L["desc"] for L in model.layers if isinstance(L.get("desc"), seqops.AttnDesc)), None)
     rdesc0 = next((L["desc"] for L in model.layers if isinstance(L.get("desc"), seqops.RetentionDesc)), None)
@@ -341,7 +448,7 @@ def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, ba
     prompt = rng.integers(0, sz["vocab"], S).tolist()
     out = {"size": size, "config": {k: sz[k] for k in sz}, "layers": [l["type"] + ("+" + l["mlp"].get("kind", "ff") if l["mlp"] else "") for l in cfg["layers"]],
            "streams": cfg.get("streams", 1), "linear_weights": _linear_weights(model), "weight_bytes": model.weight_bytes}
-    if gem or tes:
+    if gem or tes or paf:
         r = cfg["layers"][1]["mlp"]
         out["experts"] = {"experts": r["router"]["experts"], "top": r["router"]["top"], "ff": r["expert"]["ff"], "shared_ff": r["shared"]["ff"], "groups": r["router"].get("groups")}
     lin_flops_tok = 2.0 * (_linear_weights(model) + 0)
@@ -376,6 +483,8 @@ def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, ba
     if gem:     # window of `chunk` positions plus one pooled entry per block of 16 wholly before it
         vis = np.minimum(pos + 1, chunk) + np.maximum(0, (pos - chunk + 1) // pool)
         scen = dict(prefill=True, entries=1, visible_keys=int(vis.sum()), kv_rows_touched=S + S // pool, attn_desc=desc0)
+    elif paf:   # a sliding window of `chunk` positions (the few kept first positions of one layer are not counted)
+        scen = dict(prefill=True, entries=1, visible_keys=int(np.minimum(pos + 1, chunk).sum()), kv_rows_touched=S, attn_desc=desc0)
     elif tes:   # every earlier position; a step of portions attends over per-head keys projected from the gathered latents
         descx = next((L["desc_x"] for L in model.layers if "desc_x" in L), desc0)
         scen = dict(prefill=True, entries=1, visible_keys=int((pos + 1).sum()), kv_rows_touched=S, attn_desc=descx, ret_desc=rdesc0)
@@ -424,7 +533,7 @@ def bench_layered(design: str, size: str, pk, S: int = 4096, ctx: int = 1024, ba
                "frac_hbm_weights_only": round(touched / (msd * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
         held = eng.cache.live[ids[0]].n_tokens
         lo = (held // chunk) * chunk
-        seen = (min(held + 1, chunk) + max(0, (held - chunk + 1) // pool)) if gem else (held + 1 if tes else held - lo + 1)
+        seen = (min(held + 1, chunk) + max(0, (held - chunk + 1) // pool)) if gem else (held + 1 if tes else (min(held + 1, chunk) if paf else held - lo + 1))
         scen = dict(prefill=False, entries=B, visible_keys=B * seen, kv_rows_touched=B * seen, attn_desc=desc0, ret_desc=rdesc0)
         row["kernels"] = kernel_table(model, eng, dec_step, scen, pk)
         out["decode"].append(row)
@@ -581,7 +690,7 @@ def run(design: str, sizes: List[str], pk, pk_kind: str, S: int = 4096, ctx: int
     for size in sizes:
         row = {"size": size}
         row[design.lower()] = bench_layered(design, size, pk, S=S, ctx=ctx, steps=steps)
-        others = {"fenorax": [], "gemosun": ["fenorax"], "teselix": ["gemosun", "fenorax"]}.get(design.lower(), ["fenorax"])
+        others = {"fenorax": [], "gemosun": ["fenorax"], "teselix": ["gemosun", "fenorax"], "pafelorn": ["gemosun", "fenorax"]}.get(design.lower(), ["fenorax"])
         for other in others:                # the closest existing layer-list models at the same sizes
             try:
                 row[other] = bench_layered(other, size, pk, S=S, ctx=ctx, steps=steps)

@@ -247,11 +247,12 @@ def test_general_prep_norms_rotation_bias(ops, full, half, bias):
 # ---- recurrences -------------------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("C", [13, 256, 1030])
 def test_min_gru_over_portions_and_reused_slots(ops, C):
-    """two sequences in portions of changing size in shared steps; the slots hold another sequence's state at the start"""
+    """two sequences in portions of changing size in shared steps (one portion longer than a group of the chunked form, portions that end inside
+    a warp's share of a group); the slots hold another sequence's state at the start"""
     W = 24
     w = {"z": bf(rnd(C, W, seed=1, scale=0.4)), "z.b": rnd(C, seed=2), "x": bf(rnd(C, W, seed=3, scale=0.5)), "x.b": rnd(C, seed=4), "g": bf(rnd(C, W, seed=5, scale=0.4)),
          "o": torch.eye(C)}
-    ha, hb = bf(rnd(40, W, seed=6)), bf(rnd(9, W, seed=7))
+    ha, hb = bf(rnd(40 + 1200, W, seed=6)), bf(rnd(9, W, seed=7))
     wd = {k: v.double() for k, v in w.items()}
     ref = {"a": O.min_gru(ha.double(), wd, ""), "b": O.min_gru(hb.double(), wd, "")}
     state = torch.full((3, C), 5.0, device=DEV)
@@ -259,7 +260,7 @@ def test_min_gru_over_portions_and_reused_slots(ops, C):
     Wst = torch.cat([w["z"], w["x"], w["g"]]).double()
     H = {"a": ha, "b": hb}
     fed, slot = {"a": 0, "b": 0}, {"a": 2, "b": 0}
-    for step in [[("a", 17), ("b", 2)], [("b", 1), ("a", 1)], [("a", 2), ("b", 6)], [("a", 20)]]:
+    for step in [[("a", 17), ("b", 2)], [("b", 1), ("a", 1)], [("a", 2), ("b", 6)], [("a", 20)], [("a", 1135)], [("a", 33)], [("a", 32)]]:
         st, keep = dev_step(ops, [(k, fed[n], slot[n], pages_for(fed[n] + k)) for n, k in step])
         h = torch.cat([H[n][fed[n]:fed[n] + k] for n, k in step])
         proj = torch.cat([torch.zeros(h.shape[0], 3), (h.double() @ Wst.T).float()], 1).to(DEV)      # columns behind three unused ones
@@ -281,7 +282,7 @@ def test_rg_lru_chain_over_portions(ops, C, blocks, taps):
     w = {"y": bf(rnd(C, W, seed=1, scale=0.4)), "y.b": rnd(C, seed=2), "x": bf(rnd(C, W, seed=3, scale=0.5)), "x.b": rnd(C, seed=4), "conv": rnd(C, taps, seed=5, scale=0.5),
          "conv.b": rnd(C, seed=6, scale=0.2), "ra": bf(rnd(blocks, bw, bw, seed=7, scale=1 / math.sqrt(bw))), "ra.b": rnd(blocks, bw, seed=8), "ri": bf(rnd(blocks, bw, bw, seed=9, scale=1 / math.sqrt(bw))),
          "ri.b": rnd(blocks, bw, seed=10), "lam": rnd(C, seed=11) - 2.0, "o": torch.eye(C)}
-    h = bf(rnd(61, W, seed=12))
+    h = bf(rnd(61 + 600, W, seed=12))
     wd = {k: v.double() for k, v in w.items()}
     ref = O.rg_lru(h.double(), wd, "", {"width": C, "blocks": blocks})
     state, cstate = torch.full((2, C), 5.0, device=DEV), torch.full((2, max(taps - 1, 1), C), 5.0, device=DEV)
@@ -291,7 +292,7 @@ def test_rg_lru_chain_over_portions(ops, C, blocks, taps):
     gb = torch.cat([w["ra.b"], w["ri.b"]], 1).reshape(-1).contiguous().to(DEV)
     sp = torch.nn.functional.softplus(w["lam"].double()).float().to(DEV)
     lo = 0
-    for n in [7, 2, 1, 1, 30, 2, 18]:
+    for n in [7, 2, 1, 1, 30, 2, 18, 530, 65, 5]:
         st, keep = dev_step(ops, [(n, lo, 1, pages_for(lo + n))])
         proj = (h[lo:lo + n].double() @ Wst.T).float().to(DEV)
         u, gates, out = torch.empty(n, C, device=DEV), torch.empty(n, 2 * C, device=DEV), torch.empty(n, C, device=DEV)
