@@ -27,6 +27,35 @@ __global__ void embed_bigram_kernel(const __nv_bfloat16* __restrict__ table, con
         }
         brow = bigram + r * W;
     }
+    if ((W & 7) == 0) {   // rows start on 16-byte boundaries: eight elements per thread and pass
+        for (int i = threadIdx.x * 8; i < W; i += blockDim.x * 8) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(row + i);
+            const uint4 bv = brow ? *reinterpret_cast<const uint4*>(brow + i) : make_uint4(0u, 0u, 0u, 0u);
+            const uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w}, bu[4] = {bv.x, bv.y, bv.z, bv.w};
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[2 * j] = __uint_as_float(ru[j] << 16) * scale + __uint_as_float(bu[j] << 16);
+                v[2 * j + 1] = __uint_as_float(ru[j] & 0xffff0000u) * scale + __uint_as_float(bu[j] & 0xffff0000u);
+            }
+            float4* xo = reinterpret_cast<float4*>(x + (int64_t)t * W + i);
+            xo[0] = make_float4(v[0], v[1], v[2], v[3]), xo[1] = make_float4(v[4], v[5], v[6], v[7]);
+            if (a && a_dtype == B200SEQ_F32) {
+                float4* ao = reinterpret_cast<float4*>(reinterpret_cast<float*>(a) + (int64_t)t * W + i);
+                ao[0] = xo[0], ao[1] = xo[1];
+            } else if (a) {
+                uint4 pk;
+                uint32_t* pu = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                    pu[j] = *reinterpret_cast<const uint32_t*>(&h2);
+                }
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a) + (int64_t)t * W + i) = pk;
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
         float v = __bfloat162float(row[i]) * scale;
         if (brow) v += __bfloat162float(brow[i]);
@@ -145,7 +174,7 @@ __global__ void diff_combine_kernel(const float* __restrict__ a, int H, int G, i
 // S_t = a_t S_(t-1) + b_t per channel, out_t = S_t * o_t; (a_t, b_t, o_t) depend on the token's own inputs only.
 // Two forms with the same result up to rounding:
 //   steps of single tokens: one thread per (entry, channel) (neighbouring threads = neighbouring channels: coalesced);
-//   steps with portions:    a block = 32 channels x 16 warps; warp w takes tokens [w * 32, w * 32 + 32) of every group of 512 tokens, keeps
+//   steps with portions:    a block = 32 channels x 16 warps; warp w takes tokens [w * 16, w * 16 + 16) of every group of 256 tokens, keeps
 //                           their (a, b, o) in registers and reduces them to (A, B) = (product of a, local end state from 0); the warps' (A, B) are
 //                           chained through shared memory to every warp's entry state, and the tokens are replayed from the registers.
 //                           Every input is read once and every output written once.
@@ -164,12 +193,17 @@ struct GruCoef {
     __device__ __forceinline__ void init(const GruArgs& a, int c) {
         bz = a.bias ? a.bias[a.z_col + c] : 0.f, bx = a.bias ? a.bias[a.x_col + c] : 0.f;
     }
-    __device__ __forceinline__ void at(const GruArgs& a, int t, int c, float& av, float& bv, float& ov) const {
+    static constexpr int NIN = 3;
+    // raw inputs of (t, c) first, arithmetic later: the chunked form issues the loads of all its tokens before it needs any of them
+    __device__ __forceinline__ void load(const GruArgs& a, int t, int c, float* r) const {
         const float* p = a.proj + (int64_t)t * a.ldp;
-        const float z = sigmoidf_acc(p[a.z_col + c] + bz);
-        const float u = p[a.x_col + c] + bx;
+        r[0] = p[a.z_col + c], r[1] = p[a.x_col + c], r[2] = p[a.g_col + c];
+    }
+    __device__ __forceinline__ void coef(const float* r, float& av, float& bv, float& ov) const {
+        const float z = sigmoidf_acc(r[0] + bz);
+        const float u = r[1] + bx;
         const float cand = u >= 0.f ? u + 0.5f : sigmoidf_acc(u);
-        av = 1.f - z, bv = z * cand, ov = siluf_acc(p[a.g_col + c]);
+        av = 1.f - z, bv = z * cand, ov = siluf_acc(r[2]);
     }
 };
 
@@ -199,13 +233,17 @@ struct LruCoef {
         by = a.bias ? a.bias[a.y_col + c] : 0.f;
         k = -a.decay_c * a.sp_lam[c];
     }
-    __device__ __forceinline__ void at(const LruArgs& a, int t, int c, float& av, float& bv, float& ov) const {
+    static constexpr int NIN = 4;
+    __device__ __forceinline__ void load(const LruArgs& a, int t, int c, float* r) const {
         const float* gp = a.gates + (int64_t)t * a.ldg;
-        const float r = sigmoidf_acc(gp[rc] + br), ig = sigmoidf_acc(gp[ic] + bi);
-        const float la = k * r;
+        r[0] = gp[rc], r[1] = gp[ic], r[2] = a.u[(int64_t)t * a.ldu + c], r[3] = a.proj[(int64_t)t * a.ldp + a.y_col + c];
+    }
+    __device__ __forceinline__ void coef(const float* r, float& av, float& bv, float& ov) const {
+        const float rg = sigmoidf_acc(r[0] + br), ig = sigmoidf_acc(r[1] + bi);
+        const float la = k * rg;
         av = expf(la);
-        bv = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * ig * a.u[(int64_t)t * a.ldu + c];   // sqrt(1 - a^2) without cancellation near a = 1
-        ov = gelu_tanhf_acc(a.proj[(int64_t)t * a.ldp + a.y_col + c] + by);
+        bv = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * ig * r[2];   // sqrt(1 - a^2) without cancellation near a = 1
+        ov = gelu_tanhf_acc(r[3] + by);
     }
 };
 
@@ -222,15 +260,16 @@ __global__ void scan_step_kernel(const Args a, const b200seq_step st) {
     k.init(a, c);
 #pragma unroll 4
     for (int t = t0; t < t1; ++t) {
-        float av, bv, ov;
-        k.at(a, t, c, av, bv, ov);
+        float r[Coef::NIN], av, bv, ov;
+        k.load(a, t, c, r);
+        k.coef(r, av, bv, ov);
         S = fmaf(av, S, bv);
         store_act(a.out, a.out_dtype, (int64_t)t * a.C + c, S * ov);
     }
     *sp = S;
 }
 
-constexpr int SC_L = 32, SC_NW = 16;
+constexpr int SC_L = 16, SC_NW = 16;
 template <typename Args, typename Coef>
 __global__ void __launch_bounds__(SC_NW * 32, 1) scan_chunk_kernel(const Args a, const b200seq_step st) {
     __shared__ float sA[SC_NW][32], sB[SC_NW][32];
@@ -247,12 +286,18 @@ __global__ void __launch_bounds__(SC_NW * 32, 1) scan_chunk_kernel(const Args a,
     k.init(a, cc);
     for (int g0 = t0; g0 < t1; g0 += SC_NW * SC_L) {
         const int base = g0 + wid * SC_L;
-        float av[SC_L], bv[SC_L], ov[SC_L];
+        float raw[SC_L][Coef::NIN], av[SC_L], bv[SC_L], ov[SC_L];
+#pragma unroll
+        for (int i = 0; i < SC_L; ++i) {   // all loads of the warp's tokens are in flight before the first is used
+#pragma unroll
+            for (int j = 0; j < Coef::NIN; ++j) raw[i][j] = 0.f;
+            if (base + i < t1) k.load(a, base + i, cc, raw[i]);
+        }
         float A = 1.f, B = 0.f;
 #pragma unroll
         for (int i = 0; i < SC_L; ++i) {
             av[i] = 1.f, bv[i] = 0.f, ov[i] = 0.f;
-            if (base + i < t1) k.at(a, base + i, cc, av[i], bv[i], ov[i]);
+            if (base + i < t1) k.coef(raw[i], av[i], bv[i], ov[i]);
             B = fmaf(av[i], B, bv[i]);
             A *= av[i];
         }
@@ -297,7 +342,7 @@ int b200seq_embed_bigram(const void* table, const void* bigram, const int32_t* i
     if (!table || !ids || !st || !x || W < 1 || (bigram && (!ent_prev || buckets < 1)) || (a && !act_dtype_ok(a_dtype)))
         return fail(B200SEQ_ERR_INVALID_ARG, "embed_bigram: bad arguments");
     if (st->T == 0) return 0;
-    embed_bigram_kernel<<<st->T, W >= 1024 ? 256 : 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)table, (const __nv_bfloat16*)bigram, ids, ent_prev, *st, scale,
+    embed_bigram_kernel<<<st->T, W >= 2048 ? 256 : 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)table, (const __nv_bfloat16*)bigram, ids, ent_prev, *st, scale,
                                                                                    buckets, mul_prev, mul_cur, W, x, a, a_dtype);
     SEQ_LAUNCH_CHECK("embed_bigram");
     return 0;

@@ -153,7 +153,7 @@ __device__ __forceinline__ float ldx(const XT* p);
 template <typename XT, bool VEC>
 __global__ void __launch_bounds__(256) moe_router_rows_kernel(const XT* __restrict__ x, int64_t ldx_, const __nv_bfloat16* __restrict__ w, int NR, int K,
                                                               float* __restrict__ z, int64_t ldz, int E, int groups, int keep, int top,
-                                                              int32_t* __restrict__ ids, float* __restrict__ wts) {
+                                                              int32_t* __restrict__ ids, float* __restrict__ wts, int kind, const float* __restrict__ corr) {
     extern __shared__ float sm[];   // NR logits, then the choice's 2 * E + groups floats
     const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const XT* xr = x + (int64_t)t * ldx_;
@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(256) moe_router_rows_kernel(const XT* __restri
         }
     }
     __syncthreads();
-    if (wid == 0) route_token(sm, sm + NR, t, lane, E, groups, keep, top, ids, wts, nullptr);
+    if (wid == 0) route_token(sm, sm + NR, t, lane, E, groups, keep, top, ids, wts, nullptr, kind, corr);
 }
 
 // grid (E), 256 threads: block e places the pairs of expert e behind those of the experts before it, in pair order
@@ -559,6 +559,12 @@ int b200seq_moe_table_route(const int32_t* table, const int32_t* tok_ids, int T,
 
 int b200seq_moe_router(const void* x, int x_dtype, int64_t ldx_, const void* w, int T, int NR, int K, int E, int groups, int keep, int top, float* z, int64_t ldz,
                        int32_t* ids, float* wts, void* stream) {
+    return b200seq_moe_router_ex(x, x_dtype, ldx_, w, T, NR, K, E, groups, keep, top, 0, nullptr, z, ldz, ids, wts, stream);
+}
+
+int b200seq_moe_router_ex(const void* x, int x_dtype, int64_t ldx_, const void* w, int T, int NR, int K, int E, int groups, int keep, int top, int kind,
+                          const float* correction, float* z, int64_t ldz, int32_t* ids, float* wts, void* stream) {
+    if (kind != 0 && kind != 1) return fail(B200SEQ_ERR_INVALID_ARG, "moe_router: score kind 0 (sigmoid) or 1 (soft-max)");
     if (!x || !w || !z || !ids || !wts || T < 0 || T > 8 || E < 1 || E > MOE_MAX_E || NR < E || K < 1 || ldx_ < K || ldz < NR || top < 1 || top > E)
         return fail(B200SEQ_ERR_INVALID_ARG, "moe_router: bad arguments (at most 8 tokens, experts <= %d)", MOE_MAX_E);
     if (groups > 1 && (E % groups || keep < 1 || keep > groups || (int64_t)keep * (E / groups) < top))
@@ -572,11 +578,11 @@ int b200seq_moe_router(const void* x, int x_dtype, int64_t ldx_, const void* w, 
     cudaStream_t cs = (cudaStream_t)stream;
     const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
     if (x_dtype == B200SEQ_F32) {
-        if (vec) moe_router_rows_kernel<float, true><<<T, 256, smem, cs>>>((const float*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts);
-        else moe_router_rows_kernel<float, false><<<T, 256, smem, cs>>>((const float*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts);
+        if (vec) moe_router_rows_kernel<float, true><<<T, 256, smem, cs>>>((const float*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts, kind, correction);
+        else moe_router_rows_kernel<float, false><<<T, 256, smem, cs>>>((const float*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts, kind, correction);
     } else {
-        if (vec) moe_router_rows_kernel<__nv_bfloat16, true><<<T, 256, smem, cs>>>((const __nv_bfloat16*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts);
-        else moe_router_rows_kernel<__nv_bfloat16, false><<<T, 256, smem, cs>>>((const __nv_bfloat16*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts);
+        if (vec) moe_router_rows_kernel<__nv_bfloat16, true><<<T, 256, smem, cs>>>((const __nv_bfloat16*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts, kind, correction);
+        else moe_router_rows_kernel<__nv_bfloat16, false><<<T, 256, smem, cs>>>((const __nv_bfloat16*)x, ldx_, wb, NR, K, z, ldz, E, g, kp, top, ids, wts, kind, correction);
     }
     SEQ_LAUNCH_CHECK("moe_router");
     return 0;

@@ -1165,6 +1165,26 @@ class LayeredModel:
         ops.embed_bigram(self.embed, self.bigram, ws.view("ids"), ws.view("prev"), st, cfg.embed_scale, int(bg[0]), int(bg[1]), int(bg[2]), x, a)
         n = len(self.layers)
         want = ws.view("want")[:R]
+        # The two branches of a mixer read the same projection and do not depend on one another: the recurrent one runs on a second stream
+        # beside the attention, a shared expert on a third beside the routed ones (inside a captured decode step they become parallel
+        # branches of the graph).  Not while operators are timed alone.
+        par = self.overlap_branches and self.dev.type == "cuda" and seqops.timeline is None
+        if par and self._side is None:
+            self._side, self._side2 = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+        main = torch.cuda.current_stream(self.dev) if par else None
+
+        def beside(stream, fn):
+            """fn on `stream` after what the main stream has queued so far; returns the event to wait for (None: it ran in line)"""
+            if not par:
+                fn()
+                return None
+            fork, done = torch.cuda.Event(), torch.cuda.Event()
+            fork.record(main)
+            stream.wait_event(fork)
+            with torch.cuda.stream(stream):
+                fn()
+                done.record(stream)
+            return done
 
         def close(L, q, last, **branches):
             """x <- x + norm_q(branches); the last sublayer of the model leaves the final norm of the wanted rows instead of the next input"""
@@ -1185,12 +1205,15 @@ class LayeredModel:
                 close(L, 1, last and not has_ff, y1=y, bias1=L["o_bias"])
             else:
                 tb: TwoBranchSpec = ls.mixer
+                right_done = beside(self._side, lambda: self._recurrent_branch(L, tb.right, ws, st, T, proj, y2))
                 self._attention_out(L, tb.left, ws, st, T, proj, y)
-                self._recurrent_branch(L, tb.right, ws, st, T, proj, y2)
+                if right_done is not None:
+                    main.wait_event(right_done)
                 close(L, 1, last and not has_ff, y1=y, bias1=L["o_bias"], w_b1=L.get("left_out"), s1=tb.left_scale, y2=y2, w_b2=L.get("right_out"), s2=tb.right_scale)
             if has_ff:
                 if isinstance(ls.ff, MoeFfSpec):
-                    self._moe_ff(L, ls.ff, ws, T, a, y, x_id=x)
+                    shared_done = beside(self._side2, lambda: self._shared_expert(L, ls.ff, ws, T, a)) if par and ls.ff.shared_ff else None
+                    self._moe_ff(L, ls.ff, ws, T, a, y, shared_done, x_id=x)
                 else:
                     z = ws.ff_proj.view(-1)[:T * ls.ff.ff].view(T, ls.ff.ff)
                     ops.linear(a, L["w_up"], z)
@@ -1371,8 +1394,11 @@ class LayeredModel:
             ops.moe_table_route(L["table"], ws.view("ids"), T, E, top, ids, wts, None if rows_form else ws.moe_cnt)
         elif f.router == "softmax":
             z = ws.moe_z[:T, :L["w_router"].shape[0]]
-            ops.linear(a, L["w_router"], z)
-            ops.moe_route_ex(z, E, 1, 1, top, ops.ROUTE_SOFTMAX, L["correction"], ids, wts, None if rows_form else ws.moe_cnt)
+            if T <= 8 and rows_form:        # few tokens: projection and choice in one kernel
+                ops.moe_router_ex(a, L["w_router"], E, 1, 1, top, ops.ROUTE_SOFTMAX, L["correction"], z, ids, wts)
+            else:
+                ops.linear(a, L["w_router"], z)
+                ops.moe_route_ex(z, E, 1, 1, top, ops.ROUTE_SOFTMAX, L["correction"], ids, wts, None if rows_form else ws.moe_cnt)
         else:
             z = ws.moe_z[:T, :L["w_router"].shape[0]]
             if T <= 8 and rows_form:        # few tokens: projection and choice in one kernel

@@ -37,7 +37,7 @@ EXPORTS = ["b200seq_last_error", "b200seq_version", "b200seq_launch_count", "b20
            "b200seq_ssm_scan", "b200seq_ssm_scratch_floats", "b200seq_argmax", "b200seq_linear_act", "b200seq_act", "b200seq_depth_norm", "b200seq_attn_prep_ex",
            "b200seq_attn_ex", "b200seq_moe_route", "b200seq_moe_sort", "b200seq_moe_linear", "b200seq_moe_gather", "b200seq_moe_combine", "b200seq_moe_router", "b200seq_moe_table_route", "b200seq_moe_linear_act", "b200seq_head_linear", "b200seq_latent_gather",
            "b200seq_latent_prep", "b200seq_rotary", "b200seq_retention", "b200seq_retention_scratch_floats", "b200seq_token_shift", "b200seq_post_norm",
-           "b200seq_moe_route_ex", "b200seq_moe_combine_ex", "b200seq_causal_conv_ex", "b200seq_embed_bigram", "b200seq_branch_norm", "b200seq_polynorm", "b200seq_softcap",
+           "b200seq_moe_route_ex", "b200seq_moe_router_ex", "b200seq_moe_combine_ex", "b200seq_causal_conv_ex", "b200seq_embed_bigram", "b200seq_branch_norm", "b200seq_polynorm", "b200seq_softcap",
            "b200seq_diff_combine", "b200seq_min_gru", "b200seq_rg_lru"]
 
 
@@ -535,6 +535,17 @@ def moe_route_ex(z: torch.Tensor, E: int, groups: int, keep: int, top: int, kind
     assert ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.is_contiguous() and wts.is_contiguous() and ids.numel() >= T * top
     assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
     _check(lib().b200seq_moe_route_ex(_p(z), C.c_int64(ldz), T, E, groups, keep, top, kind, _p(correction), _p(ids), _p(wts), _p(counts), _st(z)))
+
+
+@_timed
+def moe_router_ex(x: torch.Tensor, w: torch.Tensor, E: int, groups: int, keep: int, top: int, kind: int, correction: Optional[torch.Tensor], z: torch.Tensor,
+                  ids: torch.Tensor, wts: torch.Tensor):
+    """moe_router (projection and choice of at most 8 tokens in one kernel) with the score kind and correction of moe_route_ex"""
+    T, K, ldx = _rows2d(x)
+    _, NR, ldz = _rows2d(z)
+    assert w.dtype == torch.bfloat16 and w.is_contiguous() and tuple(w.shape) == (NR, K) and z.dtype == torch.float32 and z.shape[0] == T
+    _check(lib().b200seq_moe_router_ex(_p(x), _DT[x.dtype], C.c_int64(ldx), _p(w), T, NR, K, E, groups, keep, top, kind, _p(correction), _p(z), C.c_int64(ldz), _p(ids),
+                                       _p(wts), _st(x)))
 
 
 @_timed

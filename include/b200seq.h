@@ -320,6 +320,9 @@ int b200seq_moe_combine(const float* ys, const float* wts, const int32_t* slot_o
  * CHOICE only; the weights are the chosen s / (their sum + 1e-20).  E counts every router output, identity experts included. */
 int b200seq_moe_route_ex(const float* z, int64_t ldz, int T, int E, int groups, int keep, int top, int kind, const float* correction, int32_t* ids, float* wts,
                          int32_t* counts, void* stream);
+/* b200seq_moe_router with the score kind and correction of b200seq_moe_route_ex */
+int b200seq_moe_router_ex(const void* x, int x_dtype, int64_t ldx, const void* w_bf16, int T, int NR, int K, int E, int groups, int keep, int top, int kind,
+                          const float* correction, float* z, int64_t ldz, int32_t* ids, float* wts, void* stream);
 /* b200seq_moe_combine with identity experts: a pair whose expert id is >= E_real has no row in ys; its output is the token's own input
  * x_id[t] (f32 [T, W]) times the weight.  ids: [T * top]. */
 int b200seq_moe_combine_ex(const float* ys, const float* wts, const int32_t* slot_of, const int32_t* ids, int E_real, const float* x_id, int T, int top, int W,
