@@ -174,9 +174,10 @@ __global__ void diff_combine_kernel(const float* __restrict__ a, int H, int G, i
 // S_t = a_t S_(t-1) + b_t per channel, out_t = S_t * o_t; (a_t, b_t, o_t) depend on the token's own inputs only.
 // Two forms with the same result up to rounding:
 //   steps of single tokens: one thread per (entry, channel) (neighbouring threads = neighbouring channels: coalesced);
-//   steps with portions:    a block = 32 channels x 16 warps; warp w takes tokens [w * 16, w * 16 + 16) of every group of 256 tokens, keeps
-//                           their (a, b, o) in registers and reduces them to (A, B) = (product of a, local end state from 0); the warps' (A, B) are
-//                           chained through shared memory to every warp's entry state, and the tokens are replayed from the registers.
+//   steps with portions:    a block = 8 channels x 16 warps x 4 lanes per channel; every lane takes 16 consecutive tokens of every group of 1024,
+//                           keeps their (a, b, o) in registers and reduces them to (A, B) = (product of a, local end state from 0); the lanes'
+//                           (A, B) are chained by shuffles inside a warp and through shared memory between warps to every lane's entry state,
+//                           and the tokens are replayed from the registers.
 //                           Every input is read once and every output written once.
 struct GruArgs {
     const float* proj;
@@ -269,12 +270,13 @@ __global__ void scan_step_kernel(const Args a, const b200seq_step st) {
     *sp = S;
 }
 
-constexpr int SC_L = 16, SC_NW = 16;
+constexpr int SC_L = 16, SC_NW = 16, SC_CH = 8, SC_SUB = 32 / SC_CH;   // tokens per lane, warps, channels per block, lanes per channel in a warp
 template <typename Args, typename Coef>
 __global__ void __launch_bounds__(SC_NW * 32, 1) scan_chunk_kernel(const Args a, const b200seq_step st) {
-    __shared__ float sA[SC_NW][32], sB[SC_NW][32];
+    __shared__ float sA[SC_NW][SC_CH], sB[SC_NW][SC_CH];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const int c = blockIdx.x * 32 + lane;
+    const int ch = lane & (SC_CH - 1), sub = lane / SC_CH;
+    const int c = blockIdx.x * SC_CH + ch;
     const int e = blockIdx.y;
     const bool valid = c < a.C;
     const int cc = valid ? c : a.C - 1;
@@ -284,11 +286,11 @@ __global__ void __launch_bounds__(SC_NW * 32, 1) scan_chunk_kernel(const Args a,
     float S = st.ent_pos0[e] == 0 ? 0.f : *sp;
     Coef k;
     k.init(a, cc);
-    for (int g0 = t0; g0 < t1; g0 += SC_NW * SC_L) {
-        const int base = g0 + wid * SC_L;
+    for (int g0 = t0; g0 < t1; g0 += SC_NW * SC_SUB * SC_L) {
+        const int base = g0 + (wid * SC_SUB + sub) * SC_L;
         float raw[SC_L][Coef::NIN], av[SC_L], bv[SC_L], ov[SC_L];
 #pragma unroll
-        for (int i = 0; i < SC_L; ++i) {   // all loads of the warp's tokens are in flight before the first is used
+        for (int i = 0; i < SC_L; ++i) {   // all loads of the lane's tokens are in flight before the first is used
 #pragma unroll
             for (int j = 0; j < Coef::NIN; ++j) raw[i][j] = 0.f;
             if (base + i < t1) k.load(a, base + i, cc, raw[i]);
@@ -301,12 +303,23 @@ __global__ void __launch_bounds__(SC_NW * 32, 1) scan_chunk_kernel(const Args a,
             B = fmaf(av[i], B, bv[i]);
             A *= av[i];
         }
-        sA[wid][lane] = A, sB[wid][lane] = B;
+        // the lanes of one channel inside the warp, in token order; then the warps through shared memory
+        float As[SC_SUB], Bs[SC_SUB], WA = 1.f, WB = 0.f;
+#pragma unroll
+        for (int j = 0; j < SC_SUB; ++j) {
+            As[j] = __shfl_sync(0xffffffffu, A, ch + SC_CH * j), Bs[j] = __shfl_sync(0xffffffffu, B, ch + SC_CH * j);
+            WB = fmaf(As[j], WB, Bs[j]);
+            WA *= As[j];
+        }
+        if (sub == 0) sA[wid][ch] = WA, sB[wid][ch] = WB;
         __syncthreads();
         float s = S;
-        for (int w = 0; w < wid; ++w) s = fmaf(sA[w][lane], s, sB[w][lane]);
+        for (int w = 0; w < wid; ++w) s = fmaf(sA[w][ch], s, sB[w][ch]);
         float send = s;
-        for (int w = wid; w < SC_NW; ++w) send = fmaf(sA[w][lane], send, sB[w][lane]);
+        for (int w = wid; w < SC_NW; ++w) send = fmaf(sA[w][ch], send, sB[w][ch]);
+#pragma unroll
+        for (int j = 0; j < SC_SUB; ++j)
+            if (j < sub) s = fmaf(As[j], s, Bs[j]);
 #pragma unroll
         for (int i = 0; i < SC_L; ++i) {
             s = fmaf(av[i], s, bv[i]);
@@ -315,7 +328,7 @@ __global__ void __launch_bounds__(SC_NW * 32, 1) scan_chunk_kernel(const Args a,
         S = send;
         __syncthreads();   // sA / sB are rewritten by the next group
     }
-    if (wid == 0 && valid) *sp = S;
+    if (wid == 0 && sub == 0 && valid) *sp = S;
 }
 
 template <typename Args, typename Coef>
@@ -324,7 +337,7 @@ static int launch_scan(const Args& a, const b200seq_step* st, cudaStream_t cs) {
         const int nt = a.C >= 4096 ? 128 : (a.C >= 1024 ? 64 : 32);
         scan_step_kernel<Args, Coef><<<dim3((a.C + nt - 1) / nt, st->B), nt, 0, cs>>>(a, *st);
     } else {
-        scan_chunk_kernel<Args, Coef><<<dim3((a.C + 31) / 32, st->B), SC_NW * 32, 0, cs>>>(a, *st);
+        scan_chunk_kernel<Args, Coef><<<dim3((a.C + SC_CH - 1) / SC_CH, st->B), SC_NW * 32, 0, cs>>>(a, *st);
     }
     return 0;
 }

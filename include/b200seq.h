@@ -5,7 +5,10 @@
  * state-space recurrence with per-slot state, gated feed-forward activations, the depth-averaged residual,
  * mixtures of experts (routed or chosen by a table), retention (fixed-decay linear attention), latent
  * attention (low-rank key / value cache, soft-max sink), per-head projections, token shift and the gated
- * post-norm residual, arg-max sampling.
+ * post-norm residual, the residual with the norm on the sublayer's output and two-branch mixers, weighted
+ * q / k norms, soft-capped scores, kept first positions, differential attention, minGRU and real-gated
+ * linear recurrences, PolyNorm, soft-max routing with identity experts, a hashed bigram embedding,
+ * arg-max sampling.
  *
  * It sits beside libb200q (include/b200q.h), which holds the quantized linear layer; the conventions are
  * the same:

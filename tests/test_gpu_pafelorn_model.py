@@ -151,7 +151,7 @@ def test_whole_prompt_and_layers(cases, name):
         assert (g.double() - r).abs().max().item() < 2e-5 * r.abs().max().item()
 
 
-@pytest.mark.parametrize("name", ["mixed", "wide", "long"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "wide", "long"])
 def test_bfloat16_mode_stays_close(cases, name):
     """a portion long enough for the tensor-core paths (plain and gated epilogues, experts over sorted pairs, per-block gate projections), then single tokens"""
     c = cases(name, "bfloat16")
@@ -159,8 +159,8 @@ def test_bfloat16_mode_stays_close(cases, name):
     eng = c.engine(max_tokens=112, max_seqs=1)
     got = eng.run_entries([{"id": "a", "tokens": t[:70], "want": list(range(70))}], [])
     rows = [eng.run_entries([{"id": "a", "tokens": [t[i]], "want": [0]}], [])[0] for i in range(70, 100)]
-    if name == "mixed":
-        # one expert per token out of four: where two choice scores lie closer than the 16-bit rounding of the router's input, the choice may fall
+    if name in ("mixed", "odd"):
+        # few experts, one or two per token: where two choice scores lie closer than the 16-bit rounding of the router's input, the choice may fall
         # the other way and that row is off by a whole expert; such rows are few, all others are as close as everywhere else
         e = err_rows(np.concatenate([got, np.stack(rows)]), c.ref(t))
         assert e.median().item() < TOL16 / 4 and e.quantile(0.85).item() < TOL16
