@@ -74,7 +74,7 @@ def teselix_config(sz: dict, experts: int = 32, top: int = 4, kv_rank: int = 256
     return {"architecture": "Teselix", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "postln_alpha": 2.0, "layers": [ret, lat, dict(ret), dict(lat)]}
 
 
-def pafelorn_config(sz: dict, experts: int = 32, identity: int = 4, top: int = 4) -> dict:
+def pafelorn_config(sz: dict, experts: int = 32, identity: int = 2, top: int = 4) -> dict:
     """four out-norm layers [differential attention + dense, attention | minGRU + experts, attention | gated LRU + dense, differential attention over
     layer 0's keys and values + experts] of the size's width and head layout; windows of `chunk` positions; differential heads are half as many with
     values twice as wide; both recurrences are as wide as the model; an expert is a quarter of the dense size"""
@@ -82,16 +82,16 @@ def pafelorn_config(sz: dict, experts: int = 32, identity: int = 4, top: int = 4
     eff = sz["ff"] // 4
     moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": experts, "identity": identity, "top": top}, "shared": {"ff": eff, "limit": 7.0}}
     dense = {"kind": "dense", "ff": sz["ff"]}
-    diff = {"heads": H // 2, "kv_heads": max(G // 2, 1), "dim": D, "vdim": 2 * D, "scale": D ** -0.5, "diff": 0.5, "mask": {"size": sz["chunk"]},
-            "rot": {"dims": D, "base": 250000.0, "scaling": {"factor": 8.0}}}
+    diff = {"heads": H // 2, "kv_heads": max(G // 2, 1), "dim": D, "vdim": 2 * D, "scale": D ** -0.5, "diff": 0.2, "mask": {"size": sz["chunk"]},
+            "rot": {"dims": D, "base": 500000.0, "scaling": {"factor": 6.0}}}
     left1 = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": sz["chunk"]},
-             "rot": {"dims": D // 2, "base": 250000.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+             "rot": {"dims": D // 2, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     left2 = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 30.0, "mask": {"size": sz["chunk"], "keep_first": 4},
              "rot": {"dims": D // 2, "base": 10000.0, "scaling": {"factor": 2.0}}}
     return {"architecture": "Pafelorn", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
-            "embedding": {"scale": float(W) ** 0.5, "bigram": {"buckets": 16381, "mul_prev": 31, "mul_cur": 17}},
+            "embedding": {"scale": float(W) ** 0.5, "bigram": {"buckets": 16381, "mul_prev": 36313, "mul_cur": 27191}},
             "layers": [{"type": "attention", "mixer": diff, "mlp": dense},
-                       {"type": "parallel", "mixer": {"left": left1, "right": {"width": W}, "left_scale": 0.8, "right_scale": 0.9}, "mlp": moe},
+                       {"type": "parallel", "mixer": {"left": left1, "right": {"width": W}, "left_scale": 1.0, "right_scale": 1.0}, "mlp": moe},
                        {"type": "parallel_2", "mixer": {"left": left2, "right": {"width": W, "blocks": 8, "conv": 4}}, "mlp": dict(dense)},
                        {"type": "attention", "mixer": dict(diff, kv_from=0), "mlp": dict(moe)}]}
 

@@ -54,8 +54,9 @@ def _need(d, key: str, where: str):
     return d[key]
 
 
-def _rotary(rot, where: str, layout: str, banded: bool):
-    """banded: the scaling keeps short wavelengths, divides long ones by the factor and blends between; else every frequency is divided by the factor"""
+def _rotary(rot, where: str, layout: str):
+    """scaling with `original`: short wavelengths stay, long ones are divided by the factor, a blend between (low / high name the band);
+    scaling with a factor alone: every frequency is divided by it"""
     if rot is None:
         return None
     sc = rot.get("scaling")
@@ -64,7 +65,7 @@ def _rotary(rot, where: str, layout: str, banded: bool):
         factor = float(_need(sc, "factor", where + ".rot.scaling"))
         if factor <= 0:
             raise ConfigError(f"config: {where}: rot.scaling.factor must be positive")
-        if banded:
+        if "original" in sc or "low" in sc or "high" in sc:
             bands = (factor,) + tuple(float(_need(sc, k, where + ".rot.scaling")) for k in ("low", "high", "original"))
             if bands[2] == bands[1] or bands[1] <= 0 or bands[2] <= 0 or bands[3] <= 0:
                 raise ConfigError(f"config: {where}: rot.scaling low / high / original must be positive, low != high")
@@ -82,12 +83,12 @@ def _attention(m, where: str, kind: str) -> AttentionSpec:
                 scale=float(_need(m, "scale", where)), chunk=0, window=int(mask.get("size", 0)), qk_unit_norm=False)
     if kind == "attention":
         kv_from = m.get("kv_from")
-        spec = AttentionSpec(**base, gated=False, rot=_rotary(m.get("rot"), where, "half", False), qk_norm="head", bias=True, diff=float(_need(m, "diff", where)),
+        spec = AttentionSpec(**base, gated=False, rot=_rotary(m.get("rot"), where, "half"), qk_norm="head", bias=True, diff=float(_need(m, "diff", where)),
                              kv_from=int(kv_from) if kv_from is not None else None)
     elif kind == "parallel":
-        spec = AttentionSpec(**base, gated=False, rot=_rotary(m.get("rot"), where, "interleaved", True), qk_norm="head", bias=True, out_bias=True, head_temp=True, sink=True)
+        spec = AttentionSpec(**base, gated=False, rot=_rotary(m.get("rot"), where, "interleaved"), qk_norm="head", bias=True, out_bias=True, head_temp=True, sink=True)
     else:
-        spec = AttentionSpec(**base, gated=True, gate_elem=True, rot=_rotary(m.get("rot"), where, "interleaved", False), qk_norm="full",
+        spec = AttentionSpec(**base, gated=True, gate_elem=True, rot=_rotary(m.get("rot"), where, "interleaved"), qk_norm="full",
                              softcap=float(m.get("softcap", 0.0)), keep_first=int(mask.get("keep_first", 0)))
     if spec.heads < 1 or spec.kv_heads < 1 or spec.heads % spec.kv_heads:
         raise ConfigError(f"config: {where}: heads is not a multiple of kv_heads")

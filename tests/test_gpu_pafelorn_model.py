@@ -73,7 +73,7 @@ CONFIGS = {
                     par2(heads=4, kv_heads=2, dim=72, vdim=64, window=66, keep=70, cap=30.0, rot=24, width=128, blocks=4, conv=4, mlp=moe(experts=12, identity=0, top=2, ff=32, shared=0))],
                    vocab=130, width=96, bigram=(101, 7, 3)),
 }
-CONFIGS["long"] = config([par2(heads=4, kv_heads=2, dim=16, vdim=16, window=130, keep=5, cap=20.0, rot=8, width=64, blocks=2, conv=4, mlp=moe(experts=8, identity=2, top=3, ff=24, shared=24)),
+CONFIGS["long"] = config([par2(heads=4, kv_heads=2, dim=16, vdim=16, window=130, keep=5, cap=25.0, rot=8, width=64, blocks=2, conv=3, mlp=moe(experts=8, identity=2, top=3, ff=24, shared=24)),
                           diff(heads=4, kv_heads=1, dim=16, vdim=24, window=40, rot=16, base=10000.0, mlp=dense(96)),
                           par(heads=4, kv_heads=2, dim=24, vdim=16, window=150, rot=8, base=10000.0, width=48, mlp=moe(experts=8, identity=0, top=2, ff=24, shared=0)),
                           diff(heads=4, kv_heads=1, dim=16, vdim=24, window=70, rot=16, base=10000.0, kv_from=1, mlp=None)], vocab=77, width=64)
