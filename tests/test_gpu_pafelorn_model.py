@@ -82,7 +82,7 @@ CONFIGS["long"] = config([par2(heads=4, kv_heads=2, dim=16, vdim=16, window=130,
 # heads as wide as they come in served models: key / value tiles that need the opt-in shared memory sizes
 CONFIGS["big"] = config([par(heads=4, kv_heads=2, dim=256, vdim=256, window=80, rot=64, base=50000.0, width=72, mlp=dense(64)),
                          diff(heads=2, kv_heads=1, dim=128, vdim=256, window=50, rot=128, base=50000.0, mlp=None),
-                         par2(heads=2, kv_heads=1, dim=96, vdim=192, window=60, keep=2, cap=40.0, rot=96, width=40, blocks=5, conv=2, mlp=moe(experts=2, identity=1, top=1, ff=16, shared=16))],
+                         par2(heads=2, kv_heads=1, dim=96, vdim=160, window=60, keep=2, cap=40.0, rot=96, width=40, blocks=5, conv=2, mlp=moe(experts=2, identity=1, top=1, ff=16, shared=16))],
                         vocab=50, width=128, bigram=(11, 3, 5), cap=0.0)
 
 
