@@ -1,7 +1,9 @@
 """Python harness over the C ABI of libb200seq.so (include/b200seq.h): dense bfloat16-weight linear layers and the sequence
 operators of layer-list models (stream mixing + grouped RMS norm, carried-state causal convolutions, chunk / window attention
 over a paged KV pool, the state-space recurrence, gated activations, the depth-averaged residual, mixtures of experts, retention,
-latent attention, per-head projections, token shift + gated post-norm, arg-max).
+latent attention, per-head projections, token shift + gated post-norm, the branch sum + output norm of two-branch mixers, the bigram
+embedding, PolyNorm, soft caps, differential attention, minGRU and real-gated linear recurrences, soft-max routing with identity experts,
+arg-max).
 
 Like blazr_b200/ops.py, PyTorch is plumbing only (device memory, streams); every compute call goes through ctypes.  The library
 is compiled on first use when it is missing (`ensure_built`): a fresh checkout needs nothing but nvcc.  There is no CPU
